@@ -1,0 +1,501 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight MatMul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweep]
+
+Workload (config.workload): BASELINE config 2 -- I8 per-channel weights, K=4096, N=11008,
+f32 activations [M,4096], fused SiLU -- at M=1, the HBM-bound point the metric is quoted on.
+A step is one pass of that layer over one activation batch.  Weights rotate over replicas
+whose total size exceeds the 126 MB L2, so every step streams its weights from HBM.
+
+  value     algorithmic GB/s with inputs resident in HBM (CUDA events around K steps)
+  e2e       the same through the public API with host buffers: pinned H2D of the
+            activations and D2H of the result inside every timed step
+  roofline  algorithmic bytes per launch / average launch time vs the measured HBM peak
+  sweep     the other (format, M) points of the metric, same method (not the headline)
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank holds an 11008-column
+shard of an [4096, 11008*N] layer, activations are replicated and the outputs are
+all-gathered over NCCL: weak scaling, value = bytes all ranks streamed / max-over-ranks time.
+
+--impl reference times the reference's CPU algorithm (the oracle port) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM, N_DIM, M_HEAD = 4096, 11008, 1
+SIGMA = 0.02
+L2_BYTES = 126 * 1000 * 1000
+METRIC = "quant_matmul_i8_m1_hbm_gbs"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(fmt_bits: int, n: int, k: int, m: int, n_scales_bytes: int, bias: bool) -> int:
+    """W + S + 4*M*K + 4*M*N (+ 4*N bias): packed weights, scale/zero arrays, f32
+    activations in, f32 outputs out."""
+    return n * k * fmt_bits // 8 + n_scales_bytes + 4 * m * k + 4 * m * n + (4 * n if bias else 0)
+
+
+def philox_normal(seed, shape, sigma):
+    rng = np.random.Generator(np.random.Philox(seed))
+    return rng.standard_normal(shape, dtype=np.float32) * np.float32(sigma)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples while the GPU is under the benchmark's load."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            if ts < t0 or ts > t1 + 0.15:
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(mx)) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "warm-up + timed steps + untimed replay of the same kernel to >=1.5 s"}
+
+
+# ------------------------------------------------------------------------------ ours
+
+
+class Layer:
+    """R device replicas of one quantized weight plus an arena with activation/output slots."""
+
+    def __init__(self, backend, fnn, fmt, w_kn, m, bias=None, min_total_bytes=3 * L2_BYTES):
+        from fastnn_b200 import _lib as L
+        self.fnn, self.L, self.backend, self.fmt, self.m = fnn, L, backend, fmt, m
+        k, n = w_kn.shape
+        self.k, self.n = k, n
+        packed, scales, zeros, cb = fnn.quantize_weight_constant(w_kn, fmt)
+        zp = zeros if fmt in (L.FMT_I8, L.FMT_I4, L.FMT_F4) else np.zeros(0, np.float32)
+        meta = fnn.QuantizedWeightMeta(
+            bit_width=8 if fmt in (L.FMT_I8, L.FMT_F8) else 4, scales=scales, zero_points=zp,
+            shape=[n, k], quant_block_size=32 if fmt == L.FMT_I4CB else 0,
+            codebooks=[cb] if fmt == L.FMT_I4CB else [], fmt=fmt)
+        self.meta, self.payload = meta, packed.tobytes()
+        bits = 8 if fmt in (L.FMT_I8, L.FMT_F8) else 4
+        wbytes = n * k * bits // 8
+        self.replicas = max(2, -(-min_total_bytes // wbytes))
+        self.weights = [backend.upload_qweight(self.payload, meta) for _ in range(self.replicas)]
+        sbytes = scales.nbytes + (zp.nbytes if zp.size else 0) + (64 if fmt == L.FMT_I4CB else 0)
+        self.alg_bytes = algorithmic_bytes(bits, n, k, m, sbytes, bias is not None)
+        self.flops = 2 * m * k * n
+        al = lambda x: -(-x // 256) * 256
+        self.a_off, self.out_off = 0, al(m * k * 4)
+        self.bias_off = self.out_off + al(m * n * 4)
+        self.arena = backend.allocate_arena(self.bias_off + al(n * 4))
+        self.has_bias = bias is not None
+        if bias is not None:
+            backend.write_arena(self.arena, self.bias_off, bias.tobytes())
+
+    def set_activations(self, x):
+        self.backend.write_arena(self.arena, self.a_off, np.ascontiguousarray(x, np.float32).tobytes())
+
+    def launch(self, i, epi, path=0):
+        b = self.backend
+        rc = b.lib.fnn_cuda_qmatmul(b.ctx, self.weights[i % self.replicas].handle, self.arena.handle,
+                                    self.a_off, self.out_off, self.bias_off if self.has_bias else -1,
+                                    self.m, epi, path)
+        if rc != 0:
+            raise self.fnn.BackendError.from_status(rc)
+
+    def output(self):
+        raw = self.backend.read_arena(self.arena, self.out_off, self.m * self.n * 4)
+        return np.frombuffer(raw, np.float32).reshape(self.m, self.n)
+
+    def time_steps(self, steps, warmup, epi, path=0, min_seconds=0.0):
+        """CUDA-event time of `steps` launches replayed from one captured graph."""
+        b, lib = self.backend, self.backend.lib
+        for i in range(max(warmup, 1)):
+            self.launch(i, epi, path)
+        b.synchronize()
+        check(lib.fnn_cuda_graph_begin(b.ctx), self.fnn)
+        for i in range(steps):
+            self.launch(i, epi, path)
+        g = ctypes.c_void_p()
+        check(lib.fnn_cuda_graph_end(b.ctx, ctypes.byref(g)), self.fnn)
+        check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)  # graph warm-up (upload)
+        b.synchronize()
+        ms = ctypes.c_float()
+        check(lib.fnn_cuda_timer_start(b.ctx, 0), self.fnn)
+        check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)
+        check(lib.fnn_cuda_timer_stop(b.ctx, 0), self.fnn)
+        check(lib.fnn_cuda_timer_elapsed_ms(b.ctx, 0, ctypes.byref(ms)), self.fnn)
+        t_end = time.time() + min_seconds
+        while time.time() < t_end:  # untimed: keeps the same load up for the clock sampler
+            check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)
+            b.synchronize()
+        lib.fnn_cuda_graph_free(g)
+        return float(ms.value)
+
+    def close(self):
+        for w in self.weights:
+            w.close()
+        self.arena.close()
+
+
+def check(rc, fnn):
+    if rc != 0:
+        raise fnn.BackendError.from_status(rc)
+
+
+def run_e2e(fnn, backend, w_kn, steps, warmup):
+    """Public API, host buffers: AotExecutor.forward_pinned() = pinned H2D of x, the plan,
+    D2H of y, synchronize -- every step.  Executors rotate so weights still exceed L2."""
+    nodes = [{"op_type": "MatMul", "inputs": "[x, w]", "outputs": "[h]"},
+             {"op_type": "Silu", "inputs": "[h]", "outputs": "[y]"}]
+    n_exec = max(2, -(-3 * L2_BYTES // (K_DIM * N_DIM)))
+    execs = [fnn.AotExecutor(nodes, {"w": w_kn}, ["x"], ["y"], {"x": [M_HEAD, K_DIM]}, quantize=8,
+                             backend=backend) for _ in range(n_exec)]
+    xs = [philox_normal(100 + i, (M_HEAD, K_DIM), 1.0) for i in range(8)]
+    for e in execs:
+        e.forward({"x": xs[0]})  # first call materialises constants and captures the replay
+        e.bind_pinned()
+    for i in range(max(warmup, 3)):
+        e = execs[i % n_exec]
+        e.pinned_inputs["x"][...] = xs[i % 8]
+        e.forward_pinned()
+    launches0 = backend.launch_count()
+    t0 = time.perf_counter()
+    acc = 0.0
+    for i in range(steps):
+        e = execs[i % n_exec]
+        e.pinned_inputs["x"][...] = xs[i % 8]          # the step's input arrives in host memory
+        y = e.forward_pinned()["y"]
+        acc += float(y[0, 0])                           # the result is read on the host
+    dt = time.perf_counter() - t0
+    launches = backend.launch_count() - launches0
+    return dt / steps, launches, M_HEAD * K_DIM * 4, M_HEAD * N_DIM * 4, acc
+
+
+def cpu_baseline(w_kn, budget_s=12.0, max_iters=50):
+    """The oracle's restatement of gemm_batch_packed_simd, timed on this host."""
+    import oracle as orc
+    q = orc.quantize_kn(orc.FMT_I8, w_kn)
+    x = philox_normal(1, (M_HEAD, K_DIM), 1.0)
+    orc.qmatmul(q, x, None, orc.EPI_SILU)
+    times, t_all = [], time.perf_counter()
+    while len(times) < max_iters and time.perf_counter() - t_all < budget_s:
+        t = time.perf_counter()
+        orc.qmatmul(q, x, None, orc.EPI_SILU)
+        times.append(time.perf_counter() - t)
+    info = orc.host_info()
+    cores = info["physical_cores"] if M_HEAD >= info["physical_cores"] else 1
+    return float(np.median(times)), len(times), cores, info
+
+
+def sweep_points(L):
+    return [  # label, fmt, K, N, Ms, sigma, epilogue, bias
+        ("c2_i8", L.FMT_I8, 4096, 11008, (1, 16, 128, 512), 0.02, L.EPI_SILU, False),
+        ("c1_i4", L.FMT_I4, 4096, 4096, (1, 8), 0.02, L.EPI_NONE, True),
+        ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
+        ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
+        ("c4_i4cb_up", L.FMT_I4CB, 2048, 8192, (1, 64), 0.02, L.EPI_GELU, True),
+    ]
+
+
+def run_sweep(fnn, backend, peaks, budget_s=150.0):
+    from fastnn_b200 import _lib as L
+    out, t_start = [], time.time()
+    cache = {}
+    for label, fmt, k, n, ms, sigma, epi, has_bias in sweep_points(L):
+        if time.time() - t_start > budget_s:
+            out.append({"point": label, "skipped": "sweep time budget"})
+            continue
+        key = (k, n, sigma)
+        if key not in cache:
+            cache.clear()
+            cache[key] = philox_normal(7, (k, n), sigma)
+        w = cache[key]
+        bias = philox_normal(8, (n,), 0.01) if has_bias else None
+        for m in ms:
+            layer = Layer(backend, fnn, fmt, w, m, bias)
+            try:
+                layer.set_activations(philox_normal(9, (m, k), 1.0))
+                est = max(layer.alg_bytes / 3e12, layer.flops / 2e13)
+                steps = int(min(200, max(5, 0.05 / est)))
+                ms_total = layer.time_steps(steps, 3, epi)
+                t = ms_total / steps * 1e-3
+                gbs, tfs = layer.alg_bytes / t / 1e9, layer.flops / t / 1e12
+                out.append({"point": label, "m": m, "k": k, "n": n, "path": backend.last_path(),
+                            "us": round(t * 1e6, 2), "gbs": round(gbs, 1), "tflops": round(tfs, 2),
+                            "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
+                            "tensor_frac_bf16": round(tfs / peaks["bf16_tflops"], 3)})
+            finally:
+                layer.close()
+    return out
+
+
+def run_ours(args):
+    import torch
+    import fastnn_b200 as fnn
+    from fastnn_b200 import _lib as L
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.current_stream().cuda_stream
+    backend = fnn.CudaBackend(local, stream=stream)
+    peaks = load_peaks()
+
+    # every rank owns an 11008-column shard (seeded by rank) of the [4096, 11008*world] layer
+    w_kn = philox_normal(1000 + rank, (K_DIM, N_DIM), SIGMA)
+    layer = Layer(backend, fnn, L.FMT_I8, w_kn, M_HEAD)
+    layer.set_activations(philox_normal(1, (M_HEAD, K_DIM), 1.0))
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_load0 = time.time()
+    launches0 = backend.launch_count()
+    if world == 1:
+        ms_total = layer.time_steps(args.steps, args.warmup, L.EPI_SILU, min_seconds=1.5)
+        launches = args.steps
+    else:
+        ms_total = time_sharded(torch, dist, backend, layer, args, world, L)
+        launches = args.steps
+    t_load1 = time.time()
+    clocks = sampler.stop(t_load0, t_load1) if rank == 0 else None
+    del launches0
+
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    per_step_s = ms_total / args.steps * 1e-3
+    total_bytes = layer.alg_bytes * world
+    value = total_bytes / per_step_s / 1e9
+    path = backend.last_path()
+
+    line = None
+    if rank == 0:
+        achieved = layer.alg_bytes / per_step_s / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(per_step_s * 1e3, 6),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "config2: I8 per-channel weights K=4096 N=11008 per GPU, "
+                                   "f32 activations [1,4096], fused SiLU",
+                       "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM, "format": "i8",
+                       "kernel_path": path,
+                       "l2": f"weights rotate over {layer.replicas} replicas "
+                             f"({layer.replicas * K_DIM * N_DIM // 1000000} MB > 126 MB L2)",
+                       "parallelism": "single GPU" if world == 1 else
+                                      f"column-sharded x{world}, NCCL all-gather of outputs",
+                       "algorithmic_bytes_per_step_per_gpu": layer.alg_bytes},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": peaks["source"]},
+            "clocks": clocks, "gpu_launches": launches,
+        }
+    if world == 1:
+        e2e_s, e2e_launches, h2d, d2h, _ = run_e2e(fnn, backend, w_kn, min(args.steps, 2000),
+                                                   args.warmup)
+        line["e2e"] = {"value": round(layer.alg_bytes / e2e_s / 1e9, 1), "unit": UNIT,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "us_per_step": round(e2e_s * 1e6, 2),
+                       "api": "AotExecutor.forward_pinned (pinned H2D + plan + D2H + sync per step)"}
+        line["gpu_launches"] = launches + e2e_launches
+        t_med, iters, cores, info = cpu_baseline(w_kn)
+        line["cpu_baseline"] = {
+            "value": round(layer.alg_bytes / t_med / 1e9, 3), "unit": UNIT, "cores": cores,
+            "kind": "port",
+            "sample": f"the full M=1 layer, median of {iters} calls ({t_med * 1e3:.1f} ms each); "
+                      f"single-threaded as the reference is for M < cores; simd_level="
+                      f"{info['simd_level']}, k_tile={info['k_block_size']}"}
+        if not args.no_sweep:
+            line["sweep"] = run_sweep(fnn, backend, peaks)
+    else:
+        if rank == 0:
+            line["e2e"] = None
+    layer.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    backend.close()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
+# ncu capture summarised under profiles/ (None until a capture has been taken).
+NCU_TRAFFIC_BYTES = None
+
+
+def time_sharded(torch, dist, backend, layer, args, world, L):
+    """N > 1: shard GEMV on the compute stream, all-gather of the [M, N/g] outputs on NCCL's
+    stream, overlapped across steps with a two-deep output ring.  Barrier + synchronize on
+    both sides; CUDA events on the compute stream; the caller takes the max over ranks."""
+    m, n = layer.m, layer.n
+    ring = [torch.empty((m, n), dtype=torch.float32, device="cuda") for _ in range(2)]
+    gathered = [torch.empty((world, m, n), dtype=torch.float32, device="cuda") for _ in range(2)]
+    a_dev = torch.empty((m, layer.k), dtype=torch.float32, device="cuda")
+    a_dev.copy_(torch.from_numpy(philox_normal(1, (m, layer.k), 1.0)))
+    comm = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    lib = backend.lib
+    done = [None, None]
+
+    def step(i):
+        slot = i % 2
+        if done[slot] is not None:
+            main.wait_event(done[slot])          # the gather that read this slot has finished
+        w = layer.weights[i % layer.replicas]
+        rc = lib.fnn_cuda_qmatmul_ptr(backend.ctx, w.handle, a_dev.data_ptr(), ring[slot].data_ptr(),
+                                      None, m, L.EPI_SILU, 0)
+        if rc != 0:
+            raise RuntimeError(L.last_error())
+        ev = torch.cuda.Event()
+        ev.record(main)
+        comm.wait_event(ev)
+        with torch.cuda.stream(comm):
+            dist.all_gather_into_tensor(gathered[slot], ring[slot])
+            d = torch.cuda.Event()
+            d.record(comm)
+        done[slot] = d
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(main)
+    for i in range(args.steps):
+        step(i)
+    main.wait_stream(comm)
+    stop.record(main)
+    torch.cuda.synchronize()
+    dist.barrier()
+    return float(start.elapsed_time(stop))
+
+
+# ------------------------------------------------------------------------------ reference arm
+
+
+def run_reference(args):
+    """The reference's own CPU algorithm for the path (the oracle port of
+    gemm_batch_packed_simd; the Rust crate cannot be built here), on the host cores, same
+    workload/metric/unit.  Each step is one full M=1 layer call."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as orc
+    w_kn = philox_normal(1000, (K_DIM, N_DIM), SIGMA)
+    q = orc.quantize_kn(orc.FMT_I8, w_kn)
+    x = philox_normal(1, (M_HEAD, K_DIM), 1.0)
+    sbytes = q.scales.nbytes + q.zeros.nbytes
+    alg = algorithmic_bytes(8, N_DIM, K_DIM, M_HEAD, sbytes, False)
+    for _ in range(min(args.warmup, 3)):
+        orc.qmatmul(q, x, None, orc.EPI_SILU)
+    steps = args.steps
+    t_budget, t0, done = 120.0, time.perf_counter(), 0
+    while done < steps and time.perf_counter() - t0 < t_budget:
+        orc.qmatmul(q, x, None, orc.EPI_SILU)
+        done += 1
+    dt = (time.perf_counter() - t0) / max(done, 1)
+    info = orc.host_info()
+    value = round(alg / dt / 1e9, 3)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": done, "warmup": min(args.warmup, 3), "ms_per_step": round(dt * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "config2: I8 per-channel weights K=4096 N=11008, f32 activations "
+                               "[1,4096], fused SiLU", "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM,
+                   "format": "i8"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
+                         "sample": f"{done} full M=1 layer calls; the reference threads only when "
+                                   f"M >= physical cores ({info['physical_cores']}); simd_level="
+                                   f"{info['simd_level']}"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

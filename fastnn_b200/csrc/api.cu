@@ -1,0 +1,521 @@
+// Context, arena, plan-instruction kernels, replay and timing entry points of the C ABI.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace fnn {
+
+static thread_local char g_err[1024] = "";
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+void clear_error() { g_err[0] = 0; }
+
+int ensure_scratch(fnn_cuda_ctx *ctx, size_t bytes) {
+    if (ctx->scratch_bytes >= bytes) return FNN_OK;
+    FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
+                "scratch buffer must grow (%zu -> %zu bytes) during graph capture; run the "
+                "plan once before capturing it",
+                ctx->scratch_bytes, bytes);
+    if (ctx->scratch) {
+        FNN_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), FNN_ERR_MEMORY);
+        FNN_CUDA_CHECK(cudaFree(ctx->scratch), FNN_ERR_MEMORY);
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+    }
+    size_t want = bytes + (bytes >> 2);
+    FNN_CUDA_CHECK(cudaMalloc(&ctx->scratch, want), FNN_ERR_MEMORY);
+    ctx->scratch_bytes = want;
+    return FNN_OK;
+}
+
+// out[i] = op(a[i % a_len], b[i % b_len]); unary ops read a only.
+__global__ void elementwise_kernel(int op, const float *a, size_t a_len, const float *b,
+                                   size_t b_len, float *out, size_t out_len) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < out_len; i += stride) {
+        float x = a[i % a_len];
+        float r;
+        switch (op & 0xFF) {
+        case FNN_EW_ADD:
+            r = __fadd_rn(x, b[i % b_len]);
+            break;
+        case FNN_EW_MUL:
+            r = __fmul_rn(x, b[i % b_len]);
+            break;
+        case FNN_EW_SUB:
+            r = __fsub_rn(x, b[i % b_len]);
+            break;
+        case FNN_EW_RELU:
+            r = apply_act(x, FNN_EPI_RELU);
+            break;
+        case FNN_EW_GELU:
+            r = apply_act(x, FNN_EPI_GELU);
+            break;
+        case FNN_EW_SILU:
+            r = apply_act(x, FNN_EPI_SILU);
+            break;
+        default:
+            r = x;
+        }
+        out[i] = apply_act(r, op >> 8);
+    }
+}
+
+__global__ void fill_kernel(float *dst, size_t n, float value) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dst[i] = value;
+}
+
+__global__ void flush_kernel(uint4 *buf, size_t n, uint32_t v) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        buf[i] = make_uint4(v, v, v, v);
+}
+
+static int grid_for(const fnn_cuda_ctx *ctx, size_t work_items, int block) {
+    size_t blocks = div_ceil(work_items, (size_t)block);
+    size_t cap = (size_t)ctx->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+static bool span_ok(const fnn_cuda_arena *a, size_t off, size_t bytes) {
+    return off <= a->bytes && bytes <= a->bytes - off;
+}
+
+}  // namespace fnn
+
+using namespace fnn;
+
+extern "C" {
+
+const char *fnn_cuda_last_error(void) { return g_err; }
+
+int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) {
+    clear_error();
+    FNN_REQUIRE(out != nullptr, FNN_ERR_DISPATCH, "ctx_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    FNN_CUDA_CHECK(cudaGetDeviceCount(&count), FNN_ERR_UNSUPPORTED);
+    FNN_REQUIRE(device >= 0 && device < count, FNN_ERR_UNSUPPORTED,
+                "ctx_create: device %d not present (%d CUDA devices)", device, count);
+    FNN_CUDA_CHECK(cudaSetDevice(device), FNN_ERR_UNSUPPORTED);
+    cudaDeviceProp prop;
+    FNN_CUDA_CHECK(cudaGetDeviceProperties(&prop, device), FNN_ERR_UNSUPPORTED);
+    FNN_REQUIRE(prop.major == 10, FNN_ERR_UNSUPPORTED,
+                "ctx_create: this library is built for sm_100a only; device %d is sm_%d%d",
+                device, prop.major, prop.minor);
+    fnn_cuda_ctx *ctx = new fnn_cuda_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    ctx->total_mem = prop.totalGlobalMem;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+        ctx->owns_stream = false;
+    } else {
+        cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            delete ctx;
+            return set_error(FNN_ERR_MEMORY, "cudaStreamCreate failed: %s", cudaGetErrorString(e));
+        }
+        ctx->owns_stream = true;
+    }
+    cudaError_t e = cudaMalloc((void **)&ctx->err_flag, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return set_error(FNN_ERR_MEMORY, "ctx_create: %s", cudaGetErrorString(e));
+    }
+    *out = ctx;
+    return FNN_OK;
+}
+
+int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out) {
+    return fnn_cuda_ctx_create_on_stream(device, nullptr, out);
+}
+
+int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx) {
+    if (!ctx) return FNN_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int i = 0; i < 64; ++i) {
+        if (ctx->ev_start[i]) cudaEventDestroy(ctx->ev_start[i]);
+        if (ctx->ev_stop[i]) cudaEventDestroy(ctx->ev_stop[i]);
+    }
+    if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->err_flag) cudaFree(ctx->err_flag);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return FNN_OK;
+}
+
+int fnn_cuda_sync(fnn_cuda_ctx *ctx) {
+    FNN_REQUIRE(ctx, FNN_ERR_DISPATCH, "sync: null context");
+    FNN_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), FNN_ERR_DISPATCH);
+    int flag = 0;
+    FNN_CUDA_CHECK(cudaMemcpy(&flag, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost),
+                   FNN_ERR_DISPATCH);
+    if (flag != 0) {
+        cudaMemset(ctx->err_flag, 0, sizeof(int));
+        return set_error(FNN_ERR_DISPATCH,
+                         "a kernel gave up on a bounded wait (device error flag 0x%x)", flag);
+    }
+    return FNN_OK;
+}
+
+int fnn_cuda_launch_count(fnn_cuda_ctx *ctx, uint64_t *out) {
+    FNN_REQUIRE(ctx && out, FNN_ERR_DISPATCH, "launch_count: null argument");
+    *out = ctx->launches;
+    return FNN_OK;
+}
+
+int fnn_cuda_device_info(fnn_cuda_ctx *ctx, int *sm_count, int *cc_major, int *cc_minor,
+                         size_t *total_mem) {
+    FNN_REQUIRE(ctx, FNN_ERR_DISPATCH, "device_info: null context");
+    if (sm_count) *sm_count = ctx->sm_count;
+    if (cc_major) *cc_major = ctx->cc_major;
+    if (cc_minor) *cc_minor = ctx->cc_minor;
+    if (total_mem) *total_mem = ctx->total_mem;
+    return FNN_OK;
+}
+
+// ---- arena ---------------------------------------------------------------------------
+
+int fnn_cuda_arena_alloc(fnn_cuda_ctx *ctx, size_t bytes, fnn_cuda_arena **out) {
+    clear_error();
+    FNN_REQUIRE(ctx && out, FNN_ERR_MEMORY, "arena_alloc: null argument");
+    *out = nullptr;
+    FNN_CUDA_CHECK(cudaSetDevice(ctx->device), FNN_ERR_MEMORY);
+    size_t padded = div_ceil(bytes > 0 ? bytes : 1, 256) * 256;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, padded);
+    if (e != cudaSuccess)
+        return set_error(FNN_ERR_MEMORY, "arena_alloc: cudaMalloc(%zu) failed: %s", padded,
+                         cudaGetErrorString(e));
+    e = cudaMemsetAsync(p, 0, padded, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return set_error(FNN_ERR_MEMORY, "arena_alloc: memset failed: %s", cudaGetErrorString(e));
+    }
+    fnn_cuda_arena *a = new fnn_cuda_arena();
+    a->ctx = ctx;
+    a->base = (uint8_t *)p;
+    a->bytes = bytes;
+    a->owned = true;
+    *out = a;
+    return FNN_OK;
+}
+
+int fnn_cuda_arena_wrap(fnn_cuda_ctx *ctx, void *device_ptr, size_t bytes, fnn_cuda_arena **out) {
+    clear_error();
+    FNN_REQUIRE(ctx && out && device_ptr, FNN_ERR_MEMORY, "arena_wrap: null argument");
+    FNN_REQUIRE(((uintptr_t)device_ptr & 255u) == 0, FNN_ERR_MEMORY,
+                "arena_wrap: device pointer must be 256-byte aligned");
+    fnn_cuda_arena *a = new fnn_cuda_arena();
+    a->ctx = ctx;
+    a->base = (uint8_t *)device_ptr;
+    a->bytes = bytes;
+    a->owned = false;
+    *out = a;
+    return FNN_OK;
+}
+
+int fnn_cuda_arena_free(fnn_cuda_arena *a) {
+    if (!a) return FNN_OK;
+    if (a->owned && a->base) {
+        cudaSetDevice(a->ctx->device);
+        cudaStreamSynchronize(a->ctx->stream);
+        cudaFree(a->base);
+    }
+    delete a;
+    return FNN_OK;
+}
+
+static int arena_copy(fnn_cuda_arena *a, size_t offset, void *host, size_t bytes, bool to_device,
+                      bool async) {
+    clear_error();
+    FNN_REQUIRE(a && (host || bytes == 0), FNN_ERR_MEMORY, "arena copy: null argument");
+    int rc = FNN_OK;
+    if (!span_ok(a, offset, bytes)) {
+        // Clamp like CpuBuffer does (src/backend/cpu/mod.rs:7228-7238) but report it.
+        size_t avail = offset < a->bytes ? a->bytes - offset : 0;
+        rc = set_error(FNN_ERR_MEMORY, "arena %s out of range: offset %zu + %zu > %zu",
+                       to_device ? "write" : "read", offset, bytes, a->bytes);
+        bytes = bytes < avail ? bytes : avail;
+    }
+    if (bytes == 0) return rc;
+    cudaStream_t s = a->ctx->stream;
+    cudaError_t e;
+    if (to_device)
+        e = cudaMemcpyAsync(a->base + offset, host, bytes, cudaMemcpyHostToDevice, s);
+    else
+        e = cudaMemcpyAsync(host, a->base + offset, bytes, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess)
+        return set_error(FNN_ERR_MEMORY, "arena copy failed: %s", cudaGetErrorString(e));
+    if (!async && !a->ctx->capturing) {
+        e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess)
+            return set_error(FNN_ERR_MEMORY, "arena copy sync failed: %s", cudaGetErrorString(e));
+    }
+    return rc;
+}
+
+int fnn_cuda_arena_write(fnn_cuda_arena *a, size_t offset, const void *host, size_t bytes) {
+    return arena_copy(a, offset, (void *)host, bytes, true, false);
+}
+int fnn_cuda_arena_read(fnn_cuda_arena *a, size_t offset, void *host, size_t bytes) {
+    return arena_copy(a, offset, host, bytes, false, false);
+}
+int fnn_cuda_arena_write_async(fnn_cuda_arena *a, size_t offset, const void *pinned, size_t bytes) {
+    return arena_copy(a, offset, (void *)pinned, bytes, true, true);
+}
+int fnn_cuda_arena_read_async(fnn_cuda_arena *a, size_t offset, void *pinned, size_t bytes) {
+    return arena_copy(a, offset, pinned, bytes, false, true);
+}
+void *fnn_cuda_arena_device_ptr(fnn_cuda_arena *a) { return a ? a->base : nullptr; }
+size_t fnn_cuda_arena_size(fnn_cuda_arena *a) { return a ? a->bytes : 0; }
+
+int fnn_cuda_host_alloc(size_t bytes, void **out) {
+    clear_error();
+    FNN_REQUIRE(out, FNN_ERR_MEMORY, "host_alloc: out is null");
+    FNN_CUDA_CHECK(cudaHostAlloc(out, bytes > 0 ? bytes : 1, cudaHostAllocDefault), FNN_ERR_MEMORY);
+    return FNN_OK;
+}
+int fnn_cuda_host_free(void *ptr) {
+    if (ptr) cudaFreeHost(ptr);
+    return FNN_OK;
+}
+
+// ---- hot path dispatch --------------------------------------------------------------------
+
+static int qmatmul_impl(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a, float *out,
+                        const float *bias, size_t M, int epilogue, int path) {
+    FNN_REQUIRE(ctx && w, FNN_ERR_DISPATCH, "qmatmul: null handle");
+    FNN_REQUIRE(w->ctx->device == ctx->device, FNN_ERR_DISPATCH,
+                "qmatmul: weight lives on device %d, context on %d", w->ctx->device, ctx->device);
+    FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
+                "qmatmul: unknown epilogue %d", epilogue);
+    if (M == 0 || w->N == 0) return FNN_OK;
+    QmmArgs args{w, a, out, bias, M, epilogue};
+    switch (path) {
+    case FNN_PATH_AUTO:
+        if (qmm_tc_supported(w, M) && M >= 128) return launch_qmm_tc(ctx, args);
+        if (qmm_mma_supported(w, M)) return launch_qmm_mma(ctx, args);
+        return launch_qmm_rows(ctx, args);
+    case FNN_PATH_ROWS:
+        return launch_qmm_rows(ctx, args);
+    case FNN_PATH_MMA:
+        FNN_REQUIRE(qmm_mma_supported(w, M), FNN_ERR_UNSUPPORTED,
+                    "qmatmul: tensor-core skinny path does not cover fmt=%d N=%zu K=%zu M=%zu",
+                    w->fmt, w->N, w->K, M);
+        return launch_qmm_mma(ctx, args);
+    case FNN_PATH_TC:
+        FNN_REQUIRE(qmm_tc_supported(w, M), FNN_ERR_UNSUPPORTED,
+                    "qmatmul: tcgen05 path does not cover fmt=%d N=%zu K=%zu M=%zu", w->fmt,
+                    w->N, w->K, M);
+        return launch_qmm_tc(ctx, args);
+    default:
+        return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: unknown path %d", path);
+    }
+}
+
+int fnn_cuda_qmatmul(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, fnn_cuda_arena *arena,
+                     size_t a_offset, size_t out_offset, int64_t bias_offset, size_t M,
+                     int epilogue, int path) {
+    clear_error();
+    FNN_REQUIRE(ctx && w && arena, FNN_ERR_DISPATCH, "qmatmul: null handle");
+    FNN_REQUIRE((a_offset & 15u) == 0 && (out_offset & 15u) == 0, FNN_ERR_DISPATCH,
+                "qmatmul: slot offsets must be 16-byte aligned (planner aligns to 64)");
+    FNN_REQUIRE(span_ok(arena, a_offset, M * w->K * sizeof(float)), FNN_ERR_DISPATCH,
+                "qmatmul: activation slice [%zu, +%zu) outside arena of %zu bytes", a_offset,
+                M * w->K * sizeof(float), arena->bytes);
+    FNN_REQUIRE(span_ok(arena, out_offset, M * w->N * sizeof(float)), FNN_ERR_DISPATCH,
+                "qmatmul: output slice [%zu, +%zu) outside arena of %zu bytes", out_offset,
+                M * w->N * sizeof(float), arena->bytes);
+    const float *bias = nullptr;
+    if (bias_offset >= 0) {
+        FNN_REQUIRE(((size_t)bias_offset & 3u) == 0 &&
+                        span_ok(arena, (size_t)bias_offset, w->N * sizeof(float)),
+                    FNN_ERR_DISPATCH, "qmatmul: bias slice outside arena");
+        bias = (const float *)(arena->base + bias_offset);
+    }
+    return qmatmul_impl(ctx, w, (const float *)(arena->base + a_offset),
+                        (float *)(arena->base + out_offset), bias, M, epilogue, path);
+}
+
+int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
+                         float *out_dev, const float *bias_dev, size_t M, int epilogue,
+                         int path) {
+    clear_error();
+    FNN_REQUIRE(a_dev && out_dev, FNN_ERR_DISPATCH, "qmatmul_ptr: null device pointer");
+    FNN_REQUIRE(((uintptr_t)a_dev & 15u) == 0 && ((uintptr_t)out_dev & 15u) == 0,
+                FNN_ERR_DISPATCH, "qmatmul_ptr: pointers must be 16-byte aligned");
+    return qmatmul_impl(ctx, w, a_dev, out_dev, bias_dev, M, epilogue, path);
+}
+
+const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx) { return ctx ? ctx->last_path : ""; }
+
+// ---- remaining plan instructions --------------------------------------------------------------
+
+int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_t a_offset,
+                         size_t a_len, size_t b_offset, size_t b_len, size_t out_offset,
+                         size_t out_len) {
+    clear_error();
+    FNN_REQUIRE(ctx && arena, FNN_ERR_DISPATCH, "elementwise: null handle");
+    const int base = op & 0xFF, act = op >> 8;
+    bool binary = (base == FNN_EW_ADD || base == FNN_EW_MUL || base == FNN_EW_SUB);
+    bool unary = (base == FNN_EW_RELU || base == FNN_EW_GELU || base == FNN_EW_SILU);
+    FNN_REQUIRE((binary || unary) && act >= FNN_EPI_NONE && act <= FNN_EPI_SILU && (binary || act == 0),
+                FNN_ERR_UNSUPPORTED, "elementwise: unknown op 0x%x", op);
+    if (out_len == 0) return FNN_OK;
+    FNN_REQUIRE(a_len > 0 && (!binary || b_len > 0), FNN_ERR_DISPATCH,
+                "elementwise: empty operand");
+    FNN_REQUIRE(((a_offset | b_offset | out_offset) & 3u) == 0, FNN_ERR_DISPATCH,
+                "elementwise: offsets must be 4-byte aligned");
+    FNN_REQUIRE(span_ok(arena, a_offset, a_len * 4) && span_ok(arena, out_offset, out_len * 4) &&
+                    (!binary || span_ok(arena, b_offset, b_len * 4)),
+                FNN_ERR_DISPATCH, "elementwise: slice outside arena");
+    const float *a = (const float *)(arena->base + a_offset);
+    const float *b = binary ? (const float *)(arena->base + b_offset) : a;
+    float *o = (float *)(arena->base + out_offset);
+    elementwise_kernel<<<grid_for(ctx, out_len, 256), 256, 0, ctx->stream>>>(
+        op, a, a_len, b, binary ? b_len : 1, o, out_len);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    return FNN_OK;
+}
+
+int fnn_cuda_memcpy(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset,
+                    size_t src_offset, size_t bytes) {
+    clear_error();
+    FNN_REQUIRE(ctx && arena, FNN_ERR_DISPATCH, "memcpy: null handle");
+    FNN_REQUIRE(span_ok(arena, dst_offset, bytes) && span_ok(arena, src_offset, bytes),
+                FNN_ERR_DISPATCH, "memcpy: slice outside arena");
+    if (bytes == 0) return FNN_OK;
+    FNN_CUDA_CHECK(cudaMemcpyAsync(arena->base + dst_offset, arena->base + src_offset, bytes,
+                                   cudaMemcpyDeviceToDevice, ctx->stream),
+                   FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+int fnn_cuda_fill(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t offset, size_t bytes,
+                  float value) {
+    clear_error();
+    FNN_REQUIRE(ctx && arena, FNN_ERR_DISPATCH, "fill: null handle");
+    FNN_REQUIRE((offset & 3u) == 0 && span_ok(arena, offset, bytes), FNN_ERR_DISPATCH,
+                "fill: slice outside arena or misaligned");
+    size_t n = bytes / 4;
+    if (n == 0) return FNN_OK;
+    fill_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>((float *)(arena->base + offset), n,
+                                                                value);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    return FNN_OK;
+}
+
+// ---- replay and timing -------------------------------------------------------------------------
+
+int fnn_cuda_graph_begin(fnn_cuda_ctx *ctx) {
+    clear_error();
+    FNN_REQUIRE(ctx && !ctx->capturing, FNN_ERR_DISPATCH, "graph_begin: already capturing");
+    FNN_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed),
+                   FNN_ERR_DISPATCH);
+    ctx->capturing = true;
+    ctx->launches_at_capture = ctx->launches;
+    return FNN_OK;
+}
+
+int fnn_cuda_graph_end(fnn_cuda_ctx *ctx, fnn_cuda_graph **out) {
+    clear_error();
+    FNN_REQUIRE(ctx && out && ctx->capturing, FNN_ERR_DISPATCH, "graph_end: not capturing");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    FNN_CUDA_CHECK(cudaStreamEndCapture(ctx->stream, &g), FNN_ERR_DISPATCH);
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        return set_error(FNN_ERR_DISPATCH, "cudaGraphInstantiate failed: %s",
+                         cudaGetErrorString(e));
+    }
+    fnn_cuda_graph *h = new fnn_cuda_graph();
+    h->ctx = ctx;
+    h->graph = g;
+    h->exec = ex;
+    // launches recorded during capture did not run; they are counted per replay instead
+    h->launches_per_replay = ctx->launches - ctx->launches_at_capture;
+    ctx->launches = ctx->launches_at_capture;
+    *out = h;
+    return FNN_OK;
+}
+
+int fnn_cuda_graph_launch(fnn_cuda_ctx *ctx, fnn_cuda_graph *g) {
+    FNN_REQUIRE(ctx && g && g->exec, FNN_ERR_DISPATCH, "graph_launch: null handle");
+    FNN_CUDA_CHECK(cudaGraphLaunch(g->exec, ctx->stream), FNN_ERR_DISPATCH);
+    ctx->launches += g->launches_per_replay;
+    return FNN_OK;
+}
+
+int fnn_cuda_graph_free(fnn_cuda_graph *g) {
+    if (!g) return FNN_OK;
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return FNN_OK;
+}
+
+int fnn_cuda_timer_start(fnn_cuda_ctx *ctx, int slot) {
+    FNN_REQUIRE(ctx && slot >= 0 && slot < 64, FNN_ERR_DISPATCH, "timer: bad slot %d", slot);
+    if (!ctx->ev_start[slot]) {
+        FNN_CUDA_CHECK(cudaEventCreate(&ctx->ev_start[slot]), FNN_ERR_DISPATCH);
+        FNN_CUDA_CHECK(cudaEventCreate(&ctx->ev_stop[slot]), FNN_ERR_DISPATCH);
+    }
+    FNN_CUDA_CHECK(cudaEventRecord(ctx->ev_start[slot], ctx->stream), FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+int fnn_cuda_timer_stop(fnn_cuda_ctx *ctx, int slot) {
+    FNN_REQUIRE(ctx && slot >= 0 && slot < 64 && ctx->ev_stop[slot], FNN_ERR_DISPATCH,
+                "timer_stop: slot %d was never started", slot);
+    FNN_CUDA_CHECK(cudaEventRecord(ctx->ev_stop[slot], ctx->stream), FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+int fnn_cuda_timer_elapsed_ms(fnn_cuda_ctx *ctx, int slot, float *ms) {
+    FNN_REQUIRE(ctx && ms && slot >= 0 && slot < 64 && ctx->ev_stop[slot], FNN_ERR_DISPATCH,
+                "timer_elapsed: slot %d was never started", slot);
+    FNN_CUDA_CHECK(cudaEventSynchronize(ctx->ev_stop[slot]), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(cudaEventElapsedTime(ms, ctx->ev_start[slot], ctx->ev_stop[slot]),
+                   FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+int fnn_cuda_flush_l2(fnn_cuda_ctx *ctx) {
+    FNN_REQUIRE(ctx, FNN_ERR_DISPATCH, "flush_l2: null context");
+    if (!ctx->flush_buf) {
+        FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY, "flush_l2: first call during capture");
+        ctx->flush_bytes = (size_t)256 << 20;  // twice the 126 MB L2
+        FNN_CUDA_CHECK(cudaMalloc(&ctx->flush_buf, ctx->flush_bytes), FNN_ERR_MEMORY);
+    }
+    static uint32_t tick = 0;
+    size_t n = ctx->flush_bytes / sizeof(uint4);
+    flush_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>((uint4 *)ctx->flush_buf, n, ++tick);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+}  // extern "C"

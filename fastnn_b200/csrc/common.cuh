@@ -1,0 +1,188 @@
+// Shared declarations of the sm_100a backend library: handle structs, error plumbing and
+// the register-level decoders of fastnn's packed weight words.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string>
+
+#include "../../include/fastnn_cuda.h"
+
+namespace fnn {
+
+// ---- error plumbing ---------------------------------------------------------------
+int set_error(int code, const char *fmt, ...);
+void clear_error();
+
+#define FNN_CUDA_CHECK(expr, code)                                                         \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return fnn::set_error((code), "%s failed: %s (%s:%d)", #expr,                  \
+                                  cudaGetErrorString(_e), __FILE__, __LINE__);             \
+    } while (0)
+
+#define FNN_REQUIRE(cond, code, ...)                                                       \
+    do {                                                                                   \
+        if (!(cond)) return fnn::set_error((code), __VA_ARGS__);                           \
+    } while (0)
+
+static inline size_t div_ceil(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Items per u32 word (src/dtypes/*.rs `ITEMS`).
+__host__ __device__ static inline int items_per_word(int fmt) {
+    return (fmt == FNN_FMT_I8 || fmt == FNN_FMT_F8) ? 4 : 8;
+}
+static inline bool valid_fmt(int fmt) { return fmt >= FNN_FMT_I8 && fmt <= FNN_FMT_I4CB; }
+
+constexpr int kMarginWords = 16;   // SIMD margin appended by the reference packers
+constexpr int kCodebookBlock = 32; // quantization.rs:375
+
+}  // namespace fnn
+
+// ---- handles ------------------------------------------------------------------------
+
+struct fnn_cuda_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t total_mem = 0;
+    uint64_t launches = 0;
+    const char *last_path = "";
+    bool capturing = false;
+    uint64_t launches_at_capture = 0;
+    cudaEvent_t ev_start[64] = {};
+    cudaEvent_t ev_stop[64] = {};
+    void *flush_buf = nullptr;
+    size_t flush_bytes = 0;
+    // scratch for the tensor-core paths (activation conversion, split-K partials)
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    int *err_flag = nullptr;  // device flag written by bounded waits that gave up
+};
+
+struct fnn_cuda_arena {
+    fnn_cuda_ctx *ctx = nullptr;
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+    bool owned = false;
+};
+
+struct fnn_cuda_qweight {
+    fnn_cuda_ctx *ctx = nullptr;
+    int fmt = 0;
+    size_t N = 0, K = 0;
+    size_t qblock = 0;
+    size_t words_per_row = 0;   // reference row length in u32
+    size_t ld_u4 = 0;           // row stride of the row-padded layout, in 16-byte units
+    uint4 *rows = nullptr;      // row-padded layout [N][ld_u4] (reference bit order)
+    float *scales = nullptr;    // [N] (I4CB: [N][blocks_per_row])
+    float *zeros = nullptr;     // [N] or nullptr when every zero point is 0
+    float *codebook = nullptr;  // [16] for I4CB
+    size_t blocks_per_row = 0;
+    bool has_zero = false;
+    // fragment-major copy for the skinny tensor-core kernel (built on demand)
+    uint4 *frag = nullptr;
+    size_t frag_bytes = 0;
+    // tile-major copy for the tcgen05 kernel (built on demand)
+    void *tc = nullptr;
+    size_t tc_bytes = 0;
+    int tc_kind = 0;
+};
+
+struct fnn_cuda_graph {
+    fnn_cuda_ctx *ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches_per_replay = 0;
+};
+
+// ---- device-side decoders -------------------------------------------------------------
+// Each returns the exact f32 value the reference's `unpack_to_f32` produces for the lane.
+
+namespace fnn {
+
+// e4m3 -> f32 (src/dtypes/f8x4.rs:23-38).  Exponent 15 is NaN for every mantissa.
+__device__ __forceinline__ float e4m3_to_f32_exact(uint32_t byte) {
+    uint32_t mag = byte & 0x7Fu;
+    // (mag << 20) places exponent and mantissa in f32 position with bias 0+..; scaling
+    // by 2^120 rebiases (7 -> 127) and also turns the f32 subnormal into m * 2^-9.
+    float v = __uint_as_float(mag << 20) * 0x1p120f;
+    if ((mag & 0x78u) == 0x78u) v = __uint_as_float(0x7FC00000u);
+    return __uint_as_float(__float_as_uint(v) | ((byte & 0x80u) << 24));
+}
+
+// Hot-loop variant: identical on every code the reference quantizer can emit
+// (|v| <= 240, i.e. codes <= 0x77 / 0xF7); codes with exponent 15 decode as finite.
+__device__ __forceinline__ float e4m3_to_f32_fast(uint32_t byte) {
+    float v = __uint_as_float((byte & 0x7Fu) << 20) * 0x1p120f;
+    return __uint_as_float(__float_as_uint(v) | ((byte & 0x80u) << 24));
+}
+
+// e2m1 -> f32 (src/dtypes/f4x8.rs:21-39).  Code 0x8 decodes to +0.
+__device__ __forceinline__ float fp4_to_f32_exact(uint32_t code) {
+    uint32_t mag = code & 7u;
+    float v = __uint_as_float(mag << 22) * 0x1p126f;
+    uint32_t sign = (mag != 0u) ? ((code & 8u) << 28) : 0u;
+    return __uint_as_float(__float_as_uint(v) | sign);
+}
+
+// Sign-extended nibble (src/dtypes/i4x8.rs:22-30).
+__device__ __forceinline__ float i4_to_f32(uint32_t word, int i) {
+    return (float)(((int32_t)(word << (28 - 4 * i))) >> 28);
+}
+
+__device__ __forceinline__ float i8_to_f32(uint32_t word, int i) {
+    return (float)(int8_t)((word >> (8 * i)) & 0xFFu);
+}
+
+// act(x) of the fused epilogue (src/backend/cpu/mod.rs:3140-3171).
+__device__ __forceinline__ float apply_act(float x, int epi) {
+    switch (epi) {
+    case FNN_EPI_RELU:
+        return fmaxf(x, 0.0f);
+    case FNN_EPI_GELU: {
+        float x3 = x * x * x;
+        float t = tanhf(0.7978846f * (x + 0.044715f * x3));
+        return 0.5f * x * (1.0f + t);
+    }
+    case FNN_EPI_SILU:
+        return x / (1.0f + expf(-x));
+    default:
+        return x;
+    }
+}
+
+// dot*scale + zero*sum(a) with the reference's separate roundings
+// (src/backend/cpu/microkernels/mod.rs:293-295), then act(x + bias).
+__device__ __forceinline__ float finish_output(float dot, float scale, float zero, float rowsum,
+                                               bool has_bias, float bias, int epi) {
+    float x = __fadd_rn(__fmul_rn(dot, scale), __fmul_rn(zero, rowsum));
+    if (has_bias) x = __fadd_rn(x, bias);
+    return apply_act(x, epi);
+}
+
+// ---- launchers implemented in the kernel translation units ---------------------------------
+struct QmmArgs {
+    const fnn_cuda_qweight *w;
+    const float *a;    // [M,K]
+    float *out;        // [M,N]
+    const float *bias; // [N] or nullptr
+    size_t M;
+    int epilogue;
+};
+
+int launch_qmm_rows(fnn_cuda_ctx *ctx, const QmmArgs &args);
+bool qmm_mma_supported(const fnn_cuda_qweight *w, size_t M);
+int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &args);
+bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M);
+int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &args);
+void free_qweight_aux(fnn_cuda_qweight *w);
+
+int ensure_scratch(fnn_cuda_ctx *ctx, size_t bytes);
+
+}  // namespace fnn

@@ -1,0 +1,188 @@
+"""Host logic of the pipeline (fusion, quantization pass, memory plan, lowering), on CPU with a
+recording stand-in for the device.  Mirrors the structural tests of the reference:
+src/compiler/passes/quantization.rs:698-873, tests/quantized_pipeline.rs:608-620,
+tests/memory_planning_tests.rs."""
+import numpy as np
+import pytest
+
+import fastnn_b200 as fnn
+from fastnn_b200 import _lib as L
+from fastnn_b200.compiler import (GraphBuilder, GraphExecutor, TensorType, WeightDtype,
+                                  eliminate_dead_code, fuse_operators, lower_to_plan, plan_memory,
+                                  quantize_weights)
+from helpers import normal
+
+
+class RecordingBackend:
+    """Implements the Backend trait surface without a device: records what it is given."""
+
+    def __init__(self):
+        self.arena = None
+        self.dispatched = []
+
+    def name(self):
+        return "recording"
+
+    def allocate_arena(self, total_bytes):
+        self.arena = bytearray(total_bytes)
+        return self.arena
+
+    def compile(self, graph, memory_plan):
+        return lower_to_plan(graph, memory_plan)
+
+    def write_arena(self, arena, offset, data):
+        arena[offset:offset + len(data)] = bytes(data)
+
+    def read_arena(self, arena, offset, size):
+        return bytes(arena[offset:offset + size])
+
+    def dispatch(self, plan, arena, env):
+        self.dispatched.append([type(i).__name__ if not hasattr(i, "kernel_name") else i.kernel_name
+                                for i in plan.instructions])
+
+
+def linear_graph(m, k, n, bias=False, act=None, residual=False):
+    gb = GraphBuilder()
+    x = gb.input_with_dims([m, k])
+    w = gb.constant(normal(1, (k, n), 0.02), TensorType.new([k, n]))
+    y = gb.matmul(x, w)
+    if bias:
+        y = gb.add(y, gb.constant(normal(2, (n,), 0.01), TensorType.new([n])))
+    if act:
+        y = getattr(gb, act)(y)
+    if residual:
+        r = gb.input_with_dims([m, n])
+        y = gb.add(y, r)
+    g = gb.to_graph()
+    g.inputs = gb.recorded_input_ids()
+    g.outputs = [y.node_id()]
+    return g
+
+
+def compile_graph(g, wd):
+    ex = GraphExecutor(RecordingBackend())
+    return ex.compile_with_weight_dtype(g, wd)
+
+
+def kernels(plan):
+    return [i.kernel_name for i in plan.instructions if isinstance(i, fnn.CallKernel)]
+
+
+@pytest.mark.parametrize("wd,name", [(WeightDtype.I4, "matmul_i4"), (WeightDtype.I8, "matmul_i8"),
+                                     (WeightDtype.F8x4, "matmul_f8"), (WeightDtype.F4x8, "matmul_f4"),
+                                     (WeightDtype.I4Codebook, "matmul_i4")])
+def test_kernel_name_and_meta_per_weight_dtype(wd, name):
+    plan, mp, g = compile_graph(linear_graph(2, 64, 16), wd)
+    assert kernels(plan) == [name]
+    call = [i for i in plan.instructions if isinstance(i, fnn.CallKernel)][0]
+    meta = call.weight_meta
+    assert call.params[:3] == [2, 64, 16] and meta.shape == [16, 64]  # [N,K]: reversed
+    if wd == WeightDtype.I4Codebook:
+        assert meta.quant_block_size == 32 and len(meta.codebooks) == 1
+        assert meta.scales.size == 16 * 2 and meta.zero_points.size == 0
+    else:
+        assert meta.quant_block_size == 0 and meta.scales.size == 16
+    assert meta.bit_width == (8 if wd in (WeightDtype.I8, WeightDtype.F8x4) else 4)
+    # the WriteConst payload is the reference byte stream: rows + 16 margin words
+    wc = [i for i in plan.instructions if isinstance(i, fnn.WriteConst)][0]
+    items = 4 if meta.bit_width == 8 else 8
+    assert len(wc.data) == (16 * (64 // items) + 16) * 4 == wc.dst.size
+
+
+def test_only_constant_weights_are_quantized():
+    gb = GraphBuilder()
+    x = gb.input_with_dims([2, 8])
+    w = gb.input_with_dims([8, 4])  # a runtime input stays f32 (quantization.rs:47-89)
+    y = gb.matmul(x, w)
+    g = gb.to_graph()
+    g.inputs, g.outputs = gb.recorded_input_ids(), [y.node_id()]
+    quantize_weights(g, WeightDtype.I8)
+    assert all(not n.output_type.dtype.is_quantized for n in g.nodes)
+    with pytest.raises(fnn.BackendError, match="Unsupported"):
+        lower_to_plan(g, plan_memory(g))  # f32 MatMul is not this backend's path
+
+
+def test_fusion_matmul_add_act_and_op_act():
+    g = linear_graph(2, 64, 16, bias=True, act="gelu")
+    fuse_operators(g)
+    mm = [n for n in g.nodes if n.opcode.value == "MatMul"]
+    assert len(mm) == 1 and mm[0].attrs["fused_op"] == "MatMulAddGelu" and len(mm[0].inputs) == 3
+    g = linear_graph(2, 64, 16, act="silu")
+    fuse_operators(g)
+    mm = [n for n in g.nodes if n.opcode.value == "MatMul"]
+    assert mm[0].attrs["fused_op"] == "OpSilu" and len(g.nodes) == 3
+    # bias without activation is not fused by the graph passes (no MatMul+Add-only fusion)
+    g = linear_graph(2, 64, 16, bias=True)
+    fuse_operators(g)
+    assert [n.opcode.value for n in g.nodes].count("Add") == 1
+
+
+def test_lowering_keeps_the_epilogue_the_cpu_backend_drops():
+    plan, _, _ = compile_graph(linear_graph(2, 64, 16, bias=True, act="gelu"), WeightDtype.I8)
+    call = [i for i in plan.instructions if isinstance(i, fnn.CallKernel)]
+    assert len(call) == 1 and len(call[0].input_slices) == 3 and call[0].params[3] == L.EPI_GELU
+    plan, _, _ = compile_graph(linear_graph(2, 64, 16, act="silu"), WeightDtype.I8)
+    call = [i for i in plan.instructions if isinstance(i, fnn.CallKernel)]
+    assert len(call) == 1 and len(call[0].input_slices) == 2 and call[0].params[3] == L.EPI_SILU
+    # bias-only add of a 1-D constant folds into the matmul kernel (C1's MatMul+Add)
+    plan, _, _ = compile_graph(linear_graph(8, 64, 16, bias=True), WeightDtype.I4)
+    assert kernels(plan) == ["matmul_i4"]
+    # a residual add (rank 2) stays a separate elementwise instruction
+    plan, _, _ = compile_graph(linear_graph(2, 64, 16, residual=True), WeightDtype.I4)
+    assert kernels(plan) == ["matmul_i4", "add_f32"]
+
+
+def test_memory_plan_alignment_persistence_and_inplace_reuse():
+    g = linear_graph(4, 64, 16, residual=True)
+    quantize_weights(g, WeightDtype.I8)
+    mp = plan_memory(g)
+    assert all(s.offset % 64 == 0 for s in mp.slots.values())
+    spans = sorted((s.offset, s.offset + s.size, nid) for nid, s in mp.slots.items())
+    mm = [n for n in g.nodes if n.opcode.value == "MatMul"][0]
+    add = [n for n in g.nodes if n.opcode.value == "Add"][0]
+    assert mp.slots[add.id].offset == mp.slots[mm.id].offset      # in-place elementwise reuse
+    others = [(a, b) for a, b, nid in spans if nid != add.id]
+    for (a0, b0), (a1, b1) in zip(others, others[1:]):
+        assert b0 <= a1, "live slots overlap"
+    assert mp.total_size >= max(b for _, b, _ in spans)
+
+
+def test_static_plan_drops_writeconst_after_first_execute():
+    be = RecordingBackend()
+    ex = GraphExecutor(be)
+    g = linear_graph(2, 64, 16)
+    plan, mp, cg = ex.compile_with_weight_dtype(g, WeightDtype.I8)
+    x = normal(3, (2, 64), 1.0).tobytes()
+    ex.execute(cg, plan, mp, [x])
+    ex.execute(cg, plan, mp, [x])
+    assert be.dispatched[0] == ["WriteConst", "matmul_i8"] and be.dispatched[1] == ["matmul_i8"]
+
+
+def test_symbolic_batch_resolves_from_input_bytes():
+    gb = GraphBuilder()
+    x = gb.input_with_dims(["d1", 64])
+    w = gb.constant(normal(1, (64, 16), 0.02), TensorType.new([64, 16]))
+    y = gb.matmul(x, w)
+    g = gb.to_graph()
+    g.inputs, g.outputs = gb.recorded_input_ids(), [y.node_id()]
+    env = GraphExecutor.shape_env_from_inputs(g, [bytes(5 * 64 * 4)])
+    assert env["d1"] == 5
+    plan, mp, cg = compile_graph(g, WeightDtype.I8)
+    call = [i for i in plan.instructions if isinstance(i, fnn.CallKernel)][0]
+    assert call.param_dims == ["d1", 64, 16]
+    assert fnn.backend.resolve_params(call.params, call.param_dims, env, 3) == [5, 64, 16]
+    with pytest.raises(fnn.BackendError):
+        GraphExecutor.shape_env_from_inputs(g, [bytes(5 * 64 * 4 + 4)])
+
+
+def test_quantize_argument_validation():
+    assert WeightDtype.from_quantize(4) == WeightDtype.I4
+    assert WeightDtype.from_quantize("i4cb") == WeightDtype.I4Codebook
+    assert WeightDtype.from_quantize(None) == WeightDtype.F32
+    with pytest.raises(ValueError):
+        WeightDtype.from_quantize(5)
+    with pytest.raises(ValueError):
+        WeightDtype.from_quantize("fp16")
+    gb = GraphBuilder()
+    with pytest.raises(fnn.BackendError):
+        gb.compile_and_execute_with_quantize([], RecordingBackend(), [], 3)
