@@ -505,17 +505,20 @@ def lower_to_plan(graph: ComputeGraph, memory_plan: MemoryPlan) -> ExecutablePla
     order = graph.topological()
     instructions: List = []
     skip: set = set()
+    # Constants first: a kernel that folds a later node (bias add) must find its operand
+    # already materialised.
     for n in order:
-        if n.id in skip:
-            continue
-        out = _slice(memory_plan, n.id)
-        if n.opcode == Opcode.Input:
-            continue
         if n.opcode == Opcode.Constant:
+            out = _slice(memory_plan, n.id)
             if isinstance(n.value, bytes):
                 instructions.append(WriteConst(out, n.value))
             else:
                 instructions.append(Fill(out, float(n.value)))
+    for n in order:
+        if n.id in skip:
+            continue
+        out = _slice(memory_plan, n.id)
+        if n.opcode in (Opcode.Input, Opcode.Constant):
             continue
         if n.opcode == Opcode.MatMul:
             a, w = graph.get_node(n.inputs[0]), graph.get_node(n.inputs[1])
