@@ -314,7 +314,8 @@ static int qmatmul_impl(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a, 
     switch (path) {
     case FNN_PATH_AUTO:
         if (qmm_tc_supported(w, M) && M >= 128) return launch_qmm_tc(ctx, args);
-        if (qmm_mma_supported(w, M)) return launch_qmm_mma(ctx, args);
+        // tiny layers stay on the row kernel: a 16-row x 128-k fragment tile would be mostly padding
+        if (qmm_mma_supported(w, M) && w->K >= 512 && w->N >= 64) return launch_qmm_mma(ctx, args);
         return launch_qmm_rows(ctx, args);
     case FNN_PATH_ROWS:
         return launch_qmm_rows(ctx, args);

@@ -88,6 +88,8 @@ struct fnn_cuda_qweight {
     // fragment-major copy for the skinny tensor-core kernel (built on demand)
     uint4 *frag = nullptr;
     size_t frag_bytes = 0;
+    float *frag_bs = nullptr;   // I4CB block scales in fragment order
+    bool mma_ok = true;         // false when values would leave the fp16 range of that kernel
     // tile-major copy for the tcgen05 kernel (built on demand)
     void *tc = nullptr;
     size_t tc_bytes = 0;

@@ -329,3 +329,62 @@ def test_graph_replay_and_launch_count(backend):
         lib.fnn_cuda_graph_free(g)
     finally:
         rig.close()
+
+
+# ---- skinny tensor-core kernel (fragment-major weights, mma.sync, fp16 hi/lo activations) ------------
+
+MMA_SHAPES = [(512, 64), (4096, 256), (1000, 33), (45, 7), (640, 1040), (8192, 96), (2048, 272)]
+
+
+@pytest.mark.parametrize("fmt", list(orc.FMT_NAMES))
+@pytest.mark.parametrize("kn", MMA_SHAPES)
+def test_mma_kernel_parity(backend, fmt, kn):
+    k, n = kn
+    w = normal(50 + k + n, (k, n), 0.02)
+    bias = normal(60 + n, (n,), 0.01)
+    q = orc.quantize_kn(fmt, w)
+    ms = [1, 2, 4, 5, 8, 13, 16, 17, 32, 33, 64, 65, 100]
+    rig = Rig(backend, q, max(ms))
+    try:
+        for m in ms:
+            x = normal(70 + m, (m, k), 1.0)
+            b, epi = ((bias, L.EPI_GELU) if m % 2 else (None, L.EPI_SILU))
+            got = rig.run(x, b, epi, L.PATH_MMA)
+            assert backend.last_path() == "mma"
+            want = orc.qmatmul(q, x, b, epi)
+            # two-term fp16 activations (M <= 16) keep f32-grade accuracy on exact code formats;
+            # the codebook format rounds centroid*scale to fp16 and larger M uses one fp16 term
+            tol = TOL_F32 if (m <= 16 and fmt != orc.FMT_I4CB) else TOL_TC
+            err = max_err_vs_rms(got, want)
+            assert err <= tol, (orc.FMT_NAMES[fmt], kn, m, err)
+        backend.synchronize()
+    finally:
+        rig.close()
+
+
+def test_mma_kernel_is_deterministic(backend):
+    q = orc.quantize_kn(orc.FMT_I4, normal(1, (4096, 512), 0.02))
+    rig = Rig(backend, q, 4)
+    try:
+        x = normal(2, (4, 4096), 1.0)
+        a = rig.run(x, None, L.EPI_NONE, L.PATH_MMA).copy()
+        for _ in range(3):
+            assert np.array_equal(a, rig.run(x, None, L.EPI_NONE, L.PATH_MMA))
+    finally:
+        rig.close()
+
+
+def test_mma_kernel_flags_activations_outside_fp16_range(backend):
+    q = orc.quantize_kn(orc.FMT_I8, normal(1, (512, 64), 0.02))
+    rig = Rig(backend, q, 1)
+    try:
+        x = normal(2, (1, 512), 1.0)
+        x[0, 3] = 1e6
+        rig.run(x, None, L.EPI_NONE, L.PATH_MMA)
+        with pytest.raises(fnn.BackendError):
+            backend.synchronize()
+        backend.synchronize()  # the flag is cleared once reported
+        rig.run(x, None, L.EPI_NONE, L.PATH_ROWS)   # the f32 row kernel has no such limit
+        backend.synchronize()
+    finally:
+        rig.close()
