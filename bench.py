@@ -250,17 +250,23 @@ def sweep_points(L):
     return [  # label, fmt, K, N, Ms, sigma, epilogue, bias
         ("c2_i8", L.FMT_I8, 4096, 11008, (1, 16, 128, 512), 0.02, L.EPI_SILU, False),
         ("c1_i4", L.FMT_I4, 4096, 4096, (1, 8), 0.02, L.EPI_NONE, True),
+        ("c3_i4", L.FMT_I4, 8192, 28672, (1,), 0.015, L.EPI_NONE, False),
         ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
         ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
         ("c4_i4cb_up", L.FMT_I4CB, 2048, 8192, (1, 64), 0.02, L.EPI_GELU, True),
     ]
 
 
-def run_sweep(fnn, backend, peaks, budget_s=150.0):
+def run_sweep(fnn, backend, peaks, budget_s=150.0, only=None, only_m=None, steps_override=None,
+              path=0):
     from fastnn_b200 import _lib as L
     out, t_start = [], time.time()
     cache = {}
     for label, fmt, k, n, ms, sigma, epi, has_bias in sweep_points(L):
+        if only is not None:
+            if label != only:
+                continue
+            ms = tuple(m for m in ms if only_m is None or m == only_m) or (only_m,)
         if time.time() - t_start > budget_s:
             out.append({"point": label, "skipped": "sweep time budget"})
             continue
@@ -275,8 +281,8 @@ def run_sweep(fnn, backend, peaks, budget_s=150.0):
             try:
                 layer.set_activations(philox_normal(9, (m, k), 1.0))
                 est = max(layer.alg_bytes / 3e12, layer.flops / 2e13)
-                steps = int(min(200, max(5, 0.05 / est)))
-                ms_total = layer.time_steps(steps, 3, epi)
+                steps = steps_override or int(min(200, max(5, 0.05 / est)))
+                ms_total = layer.time_steps(steps, 3, epi, path)
                 t = ms_total / steps * 1e-3
                 gbs, tfs = layer.alg_bytes / t / 1e9, layer.flops / t / 1e12
                 out.append({"point": label, "m": m, "k": k, "n": n, "path": backend.last_path(),
@@ -304,6 +310,12 @@ def run_ours(args):
     stream = torch.cuda.current_stream().cuda_stream
     backend = fnn.CudaBackend(local, stream=stream)
     peaks = load_peaks()
+    if args.only:  # one sweep point only (profiling aid): prints that point and exits
+        pts = run_sweep(fnn, backend, peaks, only=args.only, only_m=args.only_m,
+                        steps_override=args.steps, path=args.path)
+        print(json.dumps({"sweep": pts}), flush=True)
+        backend.close()
+        return
 
     # every rank owns an 11008-column shard (seeded by rank) of the [4096, 11008*world] layer
     w_kn = philox_normal(1000 + rank, (K_DIM, N_DIM), SIGMA)
@@ -489,6 +501,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--only", default=None, help="run one sweep point (e.g. c3_f4) and exit")
+    ap.add_argument("--only-m", type=int, default=None, help="batch rows M for --only")
+    ap.add_argument("--path", type=int, default=0, help="kernel family for --only (0 auto, 1 rows, 2 mma, 3 tc)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -330,7 +330,10 @@ class CudaBackend:
             zeros.ctypes.data if zeros.size else None, zeros.size,
             meta.quant_block_size, cb.ctypes.data if cb is not None else None,
             ctypes.byref(h)))
-        return QWeightHandle(self, h.value, meta)
+        qw = QWeightHandle(self, h.value, meta)
+        # build the kernel layouts now, so a later graph capture finds them in place
+        _check(self.lib.fnn_cuda_qweight_prepare(self.ctx, h.value, self.path))
+        return qw
 
     def close(self) -> None:
         if getattr(self, "ctx", None):

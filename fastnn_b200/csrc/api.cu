@@ -315,7 +315,7 @@ static int qmatmul_impl(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a, 
     case FNN_PATH_AUTO:
         if (qmm_tc_supported(w, M) && M >= 128) return launch_qmm_tc(ctx, args);
         // tiny layers stay on the row kernel: a 16-row x 128-k fragment tile would be mostly padding
-        if (qmm_mma_supported(w, M) && w->K >= 512 && w->N >= 64) return launch_qmm_mma(ctx, args);
+        if (qmm_mma_supported(w, M) && auto_uses_mma(w)) return launch_qmm_mma(ctx, args);
         return launch_qmm_rows(ctx, args);
     case FNN_PATH_ROWS:
         return launch_qmm_rows(ctx, args);
@@ -369,6 +369,18 @@ int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_
 }
 
 const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx) { return ctx ? ctx->last_path : ""; }
+
+int fnn_cuda_qweight_prepare(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, int path) {
+    clear_error();
+    FNN_REQUIRE(ctx && w, FNN_ERR_DISPATCH, "qweight_prepare: null handle");
+    FNN_CUDA_CHECK(cudaSetDevice(ctx->device), FNN_ERR_MEMORY);
+    int rc = FNN_OK;
+    if (path == FNN_PATH_MMA || (path == FNN_PATH_AUTO && auto_uses_mma(w) && qmm_mma_supported(w, 1)))
+        rc = prepare_qmm_mma(ctx, w);
+    if (rc == FNN_OK && (path == FNN_PATH_TC || (path == FNN_PATH_AUTO && qmm_tc_supported(w, 128))))
+        rc = prepare_qmm_tc(ctx, w);
+    return rc;
+}
 
 // ---- remaining plan instructions --------------------------------------------------------------
 

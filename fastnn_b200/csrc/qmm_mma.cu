@@ -53,12 +53,12 @@ __device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t *>(&r);
 }
 
-// Position of element i (0..7) of an 8-group inside the staged activation tile.  I4 pairs
-// nibbles (0,4),(1,5),(2,6),(3,7) when it masks two codes at once, so the activations are
-// stored in that order; every other format decodes adjacent pairs.
+// Position of element i (0..7) of an 8-group inside the staged activation tile.  I4 and F4
+// pair nibbles (0,4),(1,5),(2,6),(3,7) when they mask two codes at once, so the activations
+// are stored in that order; the other formats decode adjacent pairs.
 template <int FMT>
 __device__ __forceinline__ int pos8(int i) {
-    return (FMT == FNN_FMT_I4) ? ((i & 3) * 2 + (i >> 2)) : i;
+    return (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4) ? ((i & 3) * 2 + (i >> 2)) : i;
 }
 
 // Staged position (in halves) of activation k within its row.
@@ -112,12 +112,14 @@ struct MmaDec<FNN_FMT_F8> {
 template <>
 struct MmaDec<FNN_FMT_F4> {
     __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *, uint32_t) {
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(
-                (__nv_fp4x2_storage_t)((w >> (8 * b)) & 0xFFu), __NV_E2M1);
-            h[b] = *reinterpret_cast<uint32_t *>(&r);
-        }
+        // e2m1 is a tiny float: its (e1 e0 m) bits dropped into fp16 bits [11:9] read as
+        // 2^(e-15)*(1+m/2) (or the subnormal m*2^-15), so one multiply by 2^14 rebiases it exactly.
+        // Nibbles i and i+4 sit at the same offset of the two halves and move with one shift.
+        const uint32_t kMag = 0x0E000E00u, kSign = 0x80008000u, kTwo14 = 0x74007400u;
+        h[0] = h2_mul(((w << 9) & kMag) | ((w << 12) & kSign), kTwo14);  // (e0,e4)
+        h[1] = h2_mul(((w << 5) & kMag) | ((w << 8) & kSign), kTwo14);   // (e1,e5)
+        h[2] = h2_mul(((w << 1) & kMag) | ((w << 4) & kSign), kTwo14);   // (e2,e6)
+        h[3] = h2_mul(((w >> 3) & kMag) | (w & kSign), kTwo14);          // (e3,e7)
     }
 };
 
@@ -154,50 +156,110 @@ struct MmaParams {
     int M, N, K;
     int KB;          // k-blocks per row (padded)
     int ntiles;      // row tiles of 16
-    int tiles_per_block;
+    int tiles_per_group;
     int Kc;          // activations staged per pass (multiple of KBLK)
     int split;       // 1: hi/lo activation split (cols m and Mh+m), Mh = 4*CG; 0: Mh = 8*CG
     int epilogue;
 };
 
+// Warp groups per block for a given number of 8-column groups (register budget).
+// (the codebook format also keeps a 32 KB lookup table in shared memory, so it runs two groups)
+__host__ __device__ constexpr int groups_for(int fmt, int cg) {
+    return cg == 1 ? (fmt == FNN_FMT_I4CB ? 2 : 3) : (cg <= 4 ? 2 : 1);
+}
+
+// Stages of each lane's private cp.async ring (weights in flight = STAGES - 1 chunks per lane).
+__host__ __device__ constexpr int stages_for(int cg) { return cg == 4 ? 2 : 3; }
+
+__device__ __forceinline__ void group_barrier(int group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kW * 32) : "memory");
+}
+
+// 16-byte global -> shared copy that bypasses registers; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// One block per SM.  Its G groups of 8 warps share the staged activations; each group streams
+// its own row tiles, splitting K across its warps.
 template <int FMT, int CG>
-__global__ void __launch_bounds__(kThreadsMma, (CG <= 2) ? 3 : (CG == 4 ? 2 : 1))
+__global__ void __launch_bounds__(groups_for(FMT, CG) * kW * 32, 1)
 qmm_mma_kernel(MmaParams p) {
     using T = FragTraits<FMT>;
     constexpr int KBLK = T::KBLK, VEC = T::VEC;
     constexpr int COLS = 8 * CG;
+    constexpr int G = groups_for(FMT, CG);
+    constexpr int NT = G * kW * 32;   // threads per block
+    constexpr int NW = G * kW;        // warps per block
+    constexpr int S = stages_for(CG);
+    constexpr int UNITS = kU * 2;     // 16-byte units per lane per chunk
     extern __shared__ __align__(16) unsigned char smem[];
     const int RS = 2 * p.Kc + T::PAD_BYTES;  // bytes per staged activation row
-    unsigned char *s_act = smem;                                         // [COLS][RS]
-    float *s_red = reinterpret_cast<float *>(s_act + (size_t)COLS * RS);  // [2][kW][CG*128]
-    float *s_out = s_red + 2 * kW * CG * 128;                            // [tiles_per_block][CG*128]
-    float *s_rs_part = s_out + (size_t)p.tiles_per_block * CG * 128;     // [kW][64]
-    float *s_rs = s_rs_part + kW * 64;                                   // [64]
-    uint32_t *s_lut = reinterpret_cast<uint32_t *>(s_rs + 64);           // I4CB: [256][32]
+    const int act_rows = p.split ? 2 * p.M : p.M;  // only real batch rows are staged
+    unsigned char *s_ring = smem;                                         // [NW][S][UNITS][32] uint4
+    float *s_ring_bs = reinterpret_cast<float *>(s_ring + (size_t)NW * S * UNITS * 512);  // I4CB only
+    unsigned char *s_act = reinterpret_cast<unsigned char *>(
+        s_ring_bs + (FMT == FNN_FMT_I4CB ? (size_t)NW * S * UNITS * 32 : 0));
+    float *s_red = reinterpret_cast<float *>(s_act + (size_t)act_rows * RS);  // [G][2][kW][CG*128]
+    float *s_out = s_red + G * 2 * kW * CG * 128;                         // [G][tiles_per_group][CG*128]
+    float *s_rs_part = s_out + (size_t)G * p.tiles_per_group * CG * 128;  // [NW][64]
+    float *s_rs = s_rs_part + NW * 64;                                    // [64]
+    float *s_meta = s_rs + 64;                                            // [G][tiles_per_group][16][3]
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(s_meta + (size_t)G * p.tiles_per_group * 48);  // I4CB: [256][32]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = warp / kW, gw = warp % kW, gtid = tid - group * kW * 32;
     const int g = lane >> 2, c = lane & 3;
     const int Mh = p.split ? 4 * CG : 8 * CG;
-    const int tile0 = blockIdx.x * p.tiles_per_block;
-    const int tiles_here = min(p.tiles_per_block, p.ntiles - tile0);
+    // group ids interleave across SMs so consecutive tiles land on different SMs
+    const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * G;
+    const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;  // tiles gg, gg+GG, ...
     const bool has_zero = p.zeros != nullptr;
+    float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
+    float *my_red = s_red + (size_t)group * 2 * kW * CG * 128;
 
-    for (int i = tid; i < p.tiles_per_block * CG * 128; i += kThreadsMma) s_out[i] = 0.0f;
+    // scale / zero / bias of the group's rows: fetched now, used by the epilogue
+    float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
+    for (int i = gtid; i < tiles_here * 16; i += kW * 32) {
+        const int n = (gg + (i >> 4) * GG) * 16 + (i & 15);
+        const bool in = n < p.N;
+        my_meta[i * 3 + 0] = (in && FMT != FNN_FMT_I4CB) ? __ldg(p.scales + n) : 1.0f;
+        my_meta[i * 3 + 1] = (in && has_zero) ? __ldg(p.zeros + n) : 0.0f;
+        my_meta[i * 3 + 2] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
+    }
+    for (int i = tid; i < G * p.tiles_per_group * CG * 128; i += NT) s_out[i] = 0.0f;
     if (tid < 64) s_rs[tid] = 0.0f;
     if (FMT == FNN_FMT_I4CB) {
-        for (int i = tid; i < 256 * 32; i += kThreadsMma) {
+        for (int i = tid; i < 256 * 32; i += NT) {
             int b = i >> 5;
             __half2 v = __floats2half2_rn(p.codebook[b & 15], p.codebook[b >> 4]);
             s_lut[i] = *reinterpret_cast<uint32_t *>(&v);
         }
     }
-    // columns that carry no batch row stay zero for the whole kernel
-    for (int col = 0; col < COLS; ++col) {
-        const bool used = p.split ? (col < p.M || (col >= Mh && col < Mh + p.M)) : (col < p.M);
-        if (used) continue;
-        uint32_t *row = reinterpret_cast<uint32_t *>(s_act + (size_t)col * RS);
-        for (int i = tid; i < RS / 4; i += kThreadsMma) row[i] = 0u;
+    // staged row holding batch column (cg*8 + g), or -1 when that column carries no batch row
+    int brow[CG];
+#pragma unroll
+    for (int cg = 0; cg < CG; ++cg) {
+        const int col = cg * 8 + g;
+        if (p.split)
+            brow[cg] = (col < Mh) ? (col < p.M ? col : -1) : (col - Mh < p.M ? p.M + col - Mh : -1);
+        else
+            brow[cg] = col < p.M ? col : -1;
     }
+    unsigned char *my_ring = s_ring + (size_t)warp * S * UNITS * 512 + lane * 16;
+    float *my_ring_bs = s_ring_bs + (size_t)warp * S * UNITS * 32 + lane;
 
     float acc[CG][4];
 #pragma unroll
@@ -205,77 +267,127 @@ qmm_mma_kernel(MmaParams p) {
 #pragma unroll
         for (int r = 0; r < 4; ++r) acc[cg][r] = 0.0f;
     int red_buf = 0;
+    const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
 
     const int Kpad = p.KB * KBLK;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
         const int kc_len = min(p.Kc, Kpad - k0);
-        __syncthreads();  // previous pass fully consumed (and the zero fills above are done)
-        // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo) ------------------------
-        for (int m = 0; m < p.M; ++m) {
-            const float *src = p.act + (size_t)m * p.K;
-            __half *row_hi = reinterpret_cast<__half *>(s_act + (size_t)m * RS);
-            __half *row_lo = reinterpret_cast<__half *>(s_act + (size_t)(Mh + m) * RS);
-            float part = 0.0f;
-            for (int k = tid; k < kc_len; k += kThreadsMma) {
-                float a = (k0 + k < p.K) ? __ldg(src + k0 + k) : 0.0f;
-                part += a;
-                if (fabsf(a) > 65000.0f) atomicOr(p.err_flag, 2);  // outside fp16 range
-                __half hi = __float2half_rn(a);
-                int pos = act_pos<FMT>(k);
-                row_hi[pos] = hi;
-                if (p.split) row_lo[pos] = __float2half_rn(a - __half2float(hi));
-            }
-            if (has_zero) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-                if (lane == 0) s_rs_part[warp * 64 + m] = part;
-            }
-        }
-        __syncthreads();
-        if (has_zero && tid < p.M) {
-            float s = s_rs[tid];
-#pragma unroll
-            for (int w = 0; w < kW; ++w) s += s_rs_part[w * 64 + tid];
-            s_rs[tid] = s;
-        }
-
-        // ---- stream this K range of every tile of the block -------------------------------
         const int KBc = kc_len / KBLK;
         const int kb0 = k0 / KBLK;
         const int nch = (KBc + kU - 1) / kU;
         const int cpw = (nch + kW - 1) / kW;   // chunks per warp per tile
         const int nitems = tiles_here * cpw;
 
-        uint4 cur[kU][2], nxt[kU][2];
-        float cur_bs[kU][2], nxt_bs[kU][2];
-        auto load = [&](int it, uint4 (&buf)[kU][2], float (&bs)[kU][2]) {
+        // issue the async copies of item `it` into ring stage it % S (an empty group past the end)
+        auto issue = [&](int it) {
             const int tl = it / cpw;
-            const int ch = warp + (it - tl * cpw) * kW;
+            const int ch = gw + (it - tl * cpw) * kW;
+            const int st = it % S;
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
                 const int kb = ch * kU + u;
                 const bool ok = (it < nitems) && (ch < nch) && (kb < KBc);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    buf[u][h] = make_uint4(0, 0, 0, 0);
-                    bs[u][h] = 0.0f;
-                    if (ok) {
-                        size_t idx = (((size_t)(tile0 + tl) * p.KB + kb0 + kb) * 2 + h) * 32 + lane;
-                        buf[u][h] = __ldg(p.frag + idx);
-                        if (FMT == FNN_FMT_I4CB) bs[u][h] = __ldg(p.frag_bs + idx);
-                    }
+                    const size_t idx =
+                        ok ? (((size_t)(gg + tl * GG) * p.KB + kb0 + kb) * 2 + h) * 32 + lane : 0;
+                    cp_async16(my_ring + (size_t)(st * UNITS + u * 2 + h) * 512, p.frag + idx, ok ? 16 : 0);
+                    if (FMT == FNN_FMT_I4CB)
+                        cp_async4(my_ring_bs + (st * UNITS + u * 2 + h) * 32, p.frag_bs + idx, ok ? 4 : 0);
                 }
             }
+            cp_async_commit();
         };
+        // the first weights are in flight while the activations are being staged
+#pragma unroll
+        for (int i = 0; i < S - 1; ++i) issue(i);
 
-        if (nitems > 0) load(0, cur, cur_bs);
+        __syncthreads();  // previous pass fully consumed (and the fills above are done)
+        // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------
+        for (int m0 = 0; m0 < p.M; m0 += 2) {
+            float part[2] = {0.0f, 0.0f};
+            auto put = [&](int mi, int k, float a) {
+                part[mi] += a;
+                if (fabsf(a) > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
+                __half hi = __float2half_rn(a);
+                const int pos = act_pos<FMT>(k);
+                reinterpret_cast<__half *>(s_act + (size_t)(m0 + mi) * RS)[pos] = hi;
+                if (p.split)
+                    reinterpret_cast<__half *>(s_act + (size_t)(p.M + m0 + mi) * RS)[pos] =
+                        __float2half_rn(a - __half2float(hi));
+            };
+            if (vec_ok) {
+                const int n4 = kc_len / 4;
+                for (int b4 = 0; b4 < n4; b4 += 2 * NT) {
+                    float4 v[2][2];
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int i4 = b4 + q * NT + tid;
+                            const int k = k0 + i4 * 4;
+                            v[mi][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (m0 + mi < p.M && i4 < n4 && k < p.K)
+                                v[mi][q] = __ldg(reinterpret_cast<const float4 *>(
+                                    p.act + (size_t)(m0 + mi) * p.K + k));
+                        }
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int i4 = b4 + q * NT + tid;
+                            if (m0 + mi < p.M && i4 < n4) {
+                                put(mi, i4 * 4 + 0, v[mi][q].x);
+                                put(mi, i4 * 4 + 1, v[mi][q].y);
+                                put(mi, i4 * 4 + 2, v[mi][q].z);
+                                put(mi, i4 * 4 + 3, v[mi][q].w);
+                            }
+                        }
+                }
+            } else {
+                for (int mi = 0; mi < 2; ++mi) {
+                    if (m0 + mi >= p.M) break;
+                    const float *src = p.act + (size_t)(m0 + mi) * p.K;
+                    for (int k = tid; k < kc_len; k += NT)
+                        put(mi, k, (k0 + k < p.K) ? __ldg(src + k0 + k) : 0.0f);
+                }
+            }
+            if (has_zero) {
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    float v = part[mi];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                    if (lane == 0 && m0 + mi < p.M) s_rs_part[warp * 64 + m0 + mi] = v;
+                }
+            }
+        }
+        __syncthreads();
+        if (has_zero && tid < p.M) {
+            float s = s_rs[tid];
+            for (int w = 0; w < NW; ++w) s += s_rs_part[w * 64 + tid];
+            s_rs[tid] = s;
+        }
+
+        // ---- stream this K range of every tile of the group -------------------------------
         for (int it = 0; it < nitems; ++it) {
-            load(it + 1, nxt, nxt_bs);
+            issue(it + S - 1);
+            cp_async_wait<S - 1>();  // item `it` has landed in this lane's ring
             const int tl = it / cpw;
-            const int ch = warp + (it - tl * cpw) * kW;
+            const int ch = gw + (it - tl * cpw) * kW;
+            uint4 cur[kU][2];
+            float cur_bs[kU][2];
+#pragma unroll
+            for (int u = 0; u < kU; ++u)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int slot = (it % S) * UNITS + u * 2 + h;
+                    cur[u][h] = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
+                    cur_bs[u][h] = (FMT == FNN_FMT_I4CB) ? my_ring_bs[slot * 32] : 0.0f;
+                }
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
-                const int kb = ch * kU + u;  // may be past the range: weights are zero then
+                const int kb = ch * kU + u;  // may be past the range: the weights are zero then
                 const int kb_s = min(kb, KBc - 1);
                 // byte offset of this lane's first B vector of the k-block in a staged row
                 const int voff = T::four_bit ? (kb_s * KBLK + c * 8) * 2 : (kb_s * KBLK + c * 16) * 2;
@@ -309,66 +421,62 @@ qmm_mma_kernel(MmaParams p) {
                     const int boff = voff + (T::four_bit ? v * 64 : v * 16);
 #pragma unroll
                     for (int cg = 0; cg < CG; ++cg) {
-                        const uint4 b = *reinterpret_cast<const uint4 *>(
-                            s_act + (size_t)(cg * 8 + g) * RS + boff);
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (brow[cg] >= 0)
+                            b = *reinterpret_cast<const uint4 *>(s_act + (size_t)brow[cg] * RS + boff);
                         mma_16816(acc[cg], alo[0], ahi[0], alo[1], ahi[1], b.x, b.y);
                         mma_16816(acc[cg], alo[2], ahi[2], alo[3], ahi[3], b.z, b.w);
                     }
                 }
             }
-            // last chunk of a tile: reduce the warps' partial tiles in a fixed order
+            // last chunk of a tile: reduce the group's partial tiles in a fixed order
             if (it - tl * cpw == cpw - 1) {
-                float *red = s_red + (size_t)red_buf * kW * CG * 128;
+                float *red = my_red + (size_t)red_buf * kW * CG * 128;
 #pragma unroll
                 for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        red[(warp * CG + cg) * 128 + r * 32 + lane] = acc[cg][r];
+                        red[(gw * CG + cg) * 128 + r * 32 + lane] = acc[cg][r];
                         acc[cg][r] = 0.0f;
                     }
-                __syncthreads();
-                for (int e = tid; e < CG * 128; e += kThreadsMma) {
+                group_barrier(group);
+                for (int e = gtid; e < CG * 128; e += kW * 32) {
                     float s = 0.0f;
 #pragma unroll
                     for (int w = 0; w < kW; ++w) s += red[w * CG * 128 + e];
-                    s_out[tl * CG * 128 + e] += s;
+                    my_out[tl * CG * 128 + e] += s;
                 }
                 red_buf ^= 1;
             }
-#pragma unroll
-            for (int u = 0; u < kU; ++u)
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    cur[u][h] = nxt[u][h];
-                    cur_bs[u][h] = nxt_bs[u][h];
-                }
         }
+        cp_async_wait<0>();
     }
     __syncthreads();
 
-    // ---- epilogue: out[m][n] for the block's tiles ---------------------------------------
+    // ---- epilogue: out[m][n] for the group's tiles ---------------------------------------
     const int total = tiles_here * 16 * p.M;
-    for (int i = tid; i < total; i += kThreadsMma) {
+    for (int i = gtid; i < total; i += kW * 32) {
         const int tl = i / (16 * p.M);
         const int rem = i - tl * 16 * p.M;
         const int m = rem >> 4, r16 = rem & 15;  // consecutive threads -> consecutive n
-        const int n = (tile0 + tl) * 16 + r16;
+        const int n = (gg + tl * GG) * 16 + r16;
         if (n >= p.N) continue;
         auto frag_at = [&](int col) {
             const int cg = col >> 3, cc = col & 7;
             const int reg = (r16 >> 3) * 2 + (cc & 1);
             const int ln = (r16 & 7) * 4 + (cc >> 1);
-            return s_out[tl * CG * 128 + cg * 128 + reg * 32 + ln];
+            return my_out[tl * CG * 128 + cg * 128 + reg * 32 + ln];
         };
         float dot = frag_at(m);
         if (p.split) dot += frag_at(Mh + m);
-        const float bias = p.bias ? p.bias[n] : 0.0f;
+        const float *meta = my_meta + (tl * 16 + r16) * 3;
+        const float bias = meta[2];
         float r;
         if (FMT == FNN_FMT_I4CB) {
             r = apply_act(p.bias ? __fadd_rn(dot, bias) : dot, p.epilogue);
         } else {
-            r = finish_output(dot, p.scales[n], has_zero ? p.zeros[n] : 0.0f,
-                              has_zero ? s_rs[m] : 0.0f, p.bias != nullptr, bias, p.epilogue);
+            r = finish_output(dot, meta[0], meta[1], has_zero ? s_rs[m] : 0.0f, p.bias != nullptr,
+                              bias, p.epilogue);
         }
         p.out[(size_t)m * p.N + n] = r;
     }
@@ -440,6 +548,7 @@ int ensure_frag(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
 template <int FMT, int CG>
 int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out, int M, int split) {
     using T = FragTraits<FMT>;
+    constexpr int G = groups_for(FMT, CG);
     const fnn_cuda_qweight *w = a.w;
     MmaParams p{};
     p.frag = w->frag;
@@ -459,30 +568,40 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
     p.split = split;
     p.epilogue = a.epilogue;
 
-    // Stage as much of K as keeps two to three blocks per SM resident.
+    // One block per SM: weight ring + as much of K as fits beside the reduction buffers.
     const int Kpad = p.KB * T::KBLK;
+    const int act_rows = split ? 2 * M : M;
     const size_t lut = (FMT == FNN_FMT_I4CB) ? 256 * 32 * 4 : 0;
-    const size_t act_budget = (CG <= 2 ? 72 : 110) * 1024 - (CG <= 2 ? lut : 0);
+    const size_t ring = (size_t)G * kW * stages_for(CG) * kU * 2 * (512 + (FMT == FNN_FMT_I4CB ? 128 : 0));
+    const size_t fixed = ring + (size_t)(G * 2 * kW * CG * 128 + G * kW * 64 + 64) * 4 + lut;
+    const size_t per_tile = (size_t)G * (CG * 512 + 192);  // output accumulator + row metadata
+    const size_t out_budget = 12 * 1024;
+    const size_t cap = 226 * 1024;
+    const size_t min_act = (size_t)act_rows * (2 * T::KBLK * kU + T::PAD_BYTES);
+    FNN_REQUIRE(fixed + out_budget + min_act <= cap, FNN_ERR_UNSUPPORTED,
+                "qmatmul: shared memory budget exceeded for M=%d on the skinny tensor-core path", M);
+    const size_t act_budget = cap - fixed - out_budget;
     int Kc = Kpad;
-    while ((size_t)(8 * CG) * (2 * Kc + T::PAD_BYTES) > act_budget && Kc > T::KBLK * kU) {
+    while ((size_t)act_rows * (2 * Kc + T::PAD_BYTES) > act_budget && Kc > T::KBLK * kU) {
         Kc = (Kc / 2 + T::KBLK - 1) / T::KBLK * T::KBLK;
     }
     p.Kc = Kc;
-    const size_t act_bytes = (size_t)(8 * CG) * (2 * Kc + T::PAD_BYTES);
-    auto smem_for = [&](int tpb) {
-        return act_bytes + (size_t)(2 * kW * CG * 128 + tpb * CG * 128 + kW * 64 + 64) * 4 + lut;
-    };
-    int blocks_per_sm = (int)std::max<size_t>(1, std::min<size_t>(3, (200 * 1024) / smem_for(2)));
-    int tpb = (int)div_ceil((size_t)p.ntiles, (size_t)ctx->sm_count * blocks_per_sm);
-    if (tpb < 1) tpb = 1;
-    if (tpb > 32 / CG) tpb = 32 / CG;  // keeps the per-block output accumulator at 16 KB
-    p.tiles_per_block = tpb;
-    const size_t smem = smem_for(tpb);
-    const int grid = (int)div_ceil((size_t)p.ntiles, (size_t)tpb);
+    const size_t act_bytes = (size_t)act_rows * (2 * Kc + T::PAD_BYTES);
+    const int tpg_max = (int)std::max<size_t>(1, out_budget / per_tile);
+    int grid = ctx->sm_count;
+    int tpg = (int)div_ceil((size_t)p.ntiles, (size_t)grid * G);
+    if (tpg > tpg_max) {  // very tall layers: more blocks than SMs, run in waves
+        tpg = tpg_max;
+        grid = (int)div_ceil((size_t)p.ntiles, (size_t)G * tpg);
+    }
+    if (tpg < 1) tpg = 1;
+    grid = (int)std::min<size_t>((size_t)grid, div_ceil((size_t)p.ntiles, (size_t)G));
+    p.tiles_per_group = tpg;
+    const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
     auto kern = qmm_mma_kernel<FMT, CG>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    kern<<<grid, kThreadsMma, smem, ctx->stream>>>(p);
+    kern<<<grid, G * kW * 32, smem, ctx->stream>>>(p);
     FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
     ctx->launches++;
     return FNN_OK;
@@ -496,12 +615,13 @@ int launch_mma_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         const float *act = a.a + m0 * K;
         float *out = a.out + m0 * N;
         int rc;
+        // two-term fp16 activations while the batch fits one 8-column group (M <= 4), one term after
         if (M <= 4)
             rc = launch_mma<FMT, 1>(ctx, a, act, out, M, 1);
         else if (M <= 8)
-            rc = launch_mma<FMT, 2>(ctx, a, act, out, M, 1);
+            rc = launch_mma<FMT, 1>(ctx, a, act, out, M, 0);
         else if (M <= 16)
-            rc = launch_mma<FMT, 4>(ctx, a, act, out, M, 1);
+            rc = launch_mma<FMT, 2>(ctx, a, act, out, M, 0);
         else if (M <= 32)
             rc = launch_mma<FMT, 4>(ctx, a, act, out, M, 0);
         else
@@ -518,6 +638,8 @@ bool qmm_mma_supported(const fnn_cuda_qweight *w, size_t M) {
     (void)M;
     return w->N < (1u << 27) && w->K < (1u << 27) && w->mma_ok;
 }
+
+int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) { return ensure_frag(ctx, w); }
 
 int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     int rc = ensure_frag(ctx, const_cast<fnn_cuda_qweight *>(a.w));

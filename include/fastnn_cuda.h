@@ -128,6 +128,10 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
                             size_t N, size_t K, const float *scales, size_t n_scales,
                             const float *zeros, size_t n_zeros, size_t qblock,
                             const float *codebook16, fnn_cuda_qweight **out);
+/* Build the device layout a kernel family needs (fragment-major for FNN_PATH_MMA, tile-major
+ * for FNN_PATH_TC; FNN_PATH_AUTO builds what automatic dispatch can pick for this shape) now
+ * instead of at its first use.  Call it from Backend::compile, outside any graph capture. */
+int fnn_cuda_qweight_prepare(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, int path);
 int fnn_cuda_qweight_free(fnn_cuda_qweight *w);
 /* Reference-layout byte count: (N*ceil(K/ITEMS) + 16) * 4. */
 size_t fnn_cuda_qweight_packed_bytes(fnn_cuda_qweight *w);
