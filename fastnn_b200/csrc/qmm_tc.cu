@@ -1,9 +1,523 @@
-// tcgen05 GEMM (placeholder until the TMA/TMEM path lands).
+// tcgen05 / TMEM / TMA kernel for the quantized MatMul with natively supported weight codes:
+// I8 through kind::i8, FP8-e4m3 through kind::f8f6f4.  No weight bit is touched by an ALU: TMA
+// drops the reference's own K-contiguous rows into 128-byte-swizzled shared memory and the
+// tensor core reads them from there.
+//
+// Orientation: the weight tile is the MMA's M operand (128 output channels per CTA) and the
+// batch is its N operand, so the same kernel serves one batch row and thousands:
+//     D[n, (t,m)] += W[n, k] * Aq_t[m, k]          (accumulators in TMEM, 128 lanes = n)
+// f32 activations are first rewritten by `act_prep_kernel` as T narrow terms per element
+//   int8:  a ~= dq[m] * (128*hi + lo)             (15-bit fixed point per row, T = 2)
+//   e4m3:  a ~= dq[m] * (t1 + t2 + t3)            (three 4-bit-significand terms, T = 3)
+// which keeps the result within ~3e-4 of the f32-accumulated reference.  The epilogue reads the
+// accumulators with tcgen05.ld, recombines the terms and applies
+//     out[m,n] = act(dq[m]*scale[n]*acc + zero[n]*sum_k a[m,k] + bias[n])
+// (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
+//
+// Warp roles (192 threads): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
+// warps 2-5 = epilogue (one TMEM lane quadrant each).  Every mbarrier wait is bounded: a wait
+// that runs out raises the context's error flag, every role leaves its loop, TMEM is freed and
+// the kernel returns.
 #include "common.cuh"
+
+#include <algorithm>
+#include <cuda.h>
+#include <cuda_fp8.h>
+
 namespace fnn {
-bool qmm_tc_supported(const fnn_cuda_qweight *, size_t) { return false; }
-int prepare_qmm_tc(fnn_cuda_ctx *, fnn_cuda_qweight *) { return FNN_OK; }
-int launch_qmm_tc(fnn_cuda_ctx *, const QmmArgs &) {
-    return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path not built");
+
+namespace {
+
+constexpr int kTileN = 128;        // weight rows (output channels) per CTA tile = MMA M
+constexpr int kKBlockBytes = 128;  // bytes of K per pipeline stage = one 128B swizzle row
+constexpr int kThreadsTc = 192;
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any legitimate wait
+
+enum { KIND_I8 = 0, KIND_F8 = 1 };
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after raising the error flags) if the phase never completes or
+// another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *err_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicOr(err_flag, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
+                                            int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
+                                            int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    if (KIND == KIND_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+// 32 lanes x 16 consecutive 32-bit columns of TMEM -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled
+// (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);  // start address / 16
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                       // layout type: SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D format, A/B formats, K-major both, N (>>3) and M (>>4).
+__host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols) {
+    return (kind == KIND_I8 ? (2u << 4) | (1u << 7) | (1u << 10)   // S32 accum, signed 8-bit A and B
+                            : (1u << 4) | (0u << 7) | (0u << 10))  // F32 accum, E4M3 A and B
+           | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+}
+
+// ---- activation rewrite ---------------------------------------------------------------------
+// One block per batch row.  Writes T byte planes Bq[t][m][Kp] (rows zero-padded to Kp), the
+// per-row factor dq[m] and the row sum.
+template <int KIND>
+__global__ void __launch_bounds__(256)
+act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
+                float *__restrict__ dq, float *__restrict__ rowsum) {
+    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
+    __shared__ float s_max[8], s_sum[8];
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const float *row = act + (size_t)m * K;
+    float mx = 0.0f, sum = 0.0f;
+    for (int k = tid; k < K; k += 256) {
+        float a = row[k];
+        mx = fmaxf(mx, fabsf(a));
+        sum += a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    }
+    if ((tid & 31) == 0) {
+        s_max[tid >> 5] = mx;
+        s_sum[tid >> 5] = sum;
+    }
+    __syncthreads();
+    mx = 0.0f;
+    sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        mx = fmaxf(mx, s_max[w]);
+        sum += s_sum[w];
+    }
+    const float full = (KIND == KIND_I8) ? 16256.0f : 448.0f;
+    const float step = (mx > 0.0f && isfinite(mx)) ? mx / full : 1.0f;
+    const float inv = 1.0f / step;
+    if (tid == 0) {
+        dq[m] = step;
+        rowsum[m] = sum;
+    }
+    for (int k = tid; k < Kp; k += 256) {
+        const float x = (k < K) ? row[k] * inv : 0.0f;
+        uint8_t t[3];
+        if (KIND == KIND_I8) {
+            int q = __float2int_rn(x);
+            q = max(-16256, min(16256, q));
+            int hi = (q + 64) >> 7;
+            int lo = q - hi * 128;
+            t[0] = (uint8_t)(int8_t)hi;
+            t[1] = (uint8_t)(int8_t)lo;
+        } else {
+            float r = x;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+                t[i] = (uint8_t)c;
+                r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < T; ++i) bq[((size_t)i * Mpad + m) * Kp + k] = t[i];
+    }
+}
+
+// ---- main kernel ------------------------------------------------------------------------------
+
+struct TcParams {
+    const float *scales;
+    const float *zeros;
+    const float *bias;
+    const float *dq;
+    const float *rowsum;
+    float *out;
+    int *err_flag;
+    int M, N, K;
+    int Mb;        // batch rows per tile
+    int n_tiles, m_tiles;
+    int kblocks;   // ceil(K / 128)
+    int stages;
+    int epilogue;
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+              TcParams p) {
+    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment is what the 128B swizzle atoms need
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int BNt = T * p.Mb;                       // MMA N: (term, batch row) columns
+    const int a_bytes = kTileN * kKBlockBytes;      // 16 KB weight tile per stage
+    const int b_bytes = BNt * kKBlockBytes;         // activation tile per stage
+    const int b_stride = (b_bytes + 1023) & ~1023;
+    unsigned char *s_a = smem;
+    unsigned char *s_b = smem + (size_t)p.stages * a_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_b + (size_t)p.stages * b_stride);
+    uint64_t *full = bars, *empty = bars + p.stages;
+    uint64_t *tfull = bars + 2 * p.stages, *tempty = tfull + 2;
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(tempty + 2);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // TMEM columns: two accumulator buffers of BNt columns, power of two >= 32
+    uint32_t ncols = 32;
+    while ((int)ncols < 2 * BNt) ncols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&tfull[i], 1);
+            mbar_init(&tempty[i], 4);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(s_tmem)),
+                     "r"(ncols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    const int total_tiles = p.n_tiles * p.m_tiles;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, s_abort, p.err_flag, 0x10)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[s], (uint32_t)(a_bytes + b_bytes));
+                    tma_load_2d(s_a + (size_t)s * a_bytes, &map_w, &full[s], kb * kKBlockBytes, nt * kTileN);
+                    tma_load_3d(s_b + (size_t)s * b_stride, &map_a, &full[s], kb * kKBlockBytes, mt * p.Mb, 0);
+                    if (++s == p.stages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {  // let copies already in flight land before the CTA can exit
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(KIND, BNt);
+            int s = 0;
+            uint32_t phase = 0;
+            int as = 0;
+            uint32_t aphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&tempty[as], aphase ^ 1, s_abort, p.err_flag, 0x20)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(as * BNt);
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&full[s], phase, s_abort, p.err_flag, 0x40)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = make_desc_sw128(smem_u32(s_a + (size_t)s * a_bytes));
+                    const uint64_t db = make_desc_sw128(smem_u32(s_b + (size_t)s * b_stride));
+#pragma unroll
+                    for (int k = 0; k < kKBlockBytes / 32; ++k) {
+                        // advance both operands by 32 bytes of K inside the swizzled row
+                        tc_mma<KIND>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
+                    if (++s == p.stages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(&tfull[as]);  // accumulator complete
+                if (++as == 2) {
+                    as = 0;
+                    aphase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (4 warps, one TMEM lane quadrant each) ----------------
+        const int quad = warp & 3;
+        int as = 0;
+        uint32_t aphase = 0;
+        const bool has_zero = p.zeros != nullptr;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            if (!mbar_wait(&tfull[as], aphase, s_abort, p.err_flag, 0x80)) break;
+            tc_fence_after();
+            const int n = nt * kTileN + quad * 32 + lane;
+            const bool n_ok = n < p.N;
+            const float scale = n_ok ? p.scales[n] : 0.0f;
+            const float zero = (n_ok && has_zero) ? p.zeros[n] : 0.0f;
+            const float bias = (n_ok && p.bias) ? p.bias[n] : 0.0f;
+            const uint32_t t_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BNt);
+            for (int c0 = 0; c0 < p.Mb; c0 += 16) {
+                uint32_t r[T][16];
+#pragma unroll
+                for (int t = 0; t < T; ++t) tmem_ld16(t_base + (uint32_t)(t * p.Mb + c0), r[t]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = mt * p.Mb + c0 + j;
+                    if (m >= p.M || c0 + j >= p.Mb) continue;
+                    float acc;
+                    if (KIND == KIND_I8)
+                        acc = (float)(int)r[0][j] * 128.0f + (float)(int)r[1][j];
+                    else
+                        acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) + __uint_as_float(r[2][j]);
+                    const float dot = acc * p.dq[m];
+                    const float v = finish_output(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
+                                                  p.bias != nullptr, bias, p.epilogue);
+                    if (n_ok) p.out[(size_t)m * p.N + n] = v;  // a warp writes 32 consecutive n
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[as]);
+            if (++as == 2) {
+                as = 0;
+                aphase ^= 1;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols)
+                     : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+struct TcWeightMaps {
+    CUtensorMap w;
+};
+
+int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
+               const cuuint32_t *box) {
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims,
+                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        const char *msg = nullptr;
+        cuGetErrorString(r, &msg);
+        return set_error(FNN_ERR_DISPATCH, "cuTensorMapEncodeTiled failed: %s", msg ? msg : "?");
+    }
+    return FNN_OK;
+}
+
+template <int KIND>
+int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
+    const fnn_cuda_qweight *w = a.w;
+    const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
+    const int Kp = (K + 15) & ~15;  // TMA strides are multiples of 16 bytes
+    // batch rows per tile: T*Mb is the MMA N (multiple of 16, at most 256)
+    const int mb_max = (KIND == KIND_I8) ? 128 : 80;
+    int Mb = std::min(mb_max, (M + 15) & ~15);
+    const int m_tiles = (M + Mb - 1) / Mb;
+    const int Mpad = m_tiles * Mb;
+
+    // scratch: Bq[T][Mpad][Kp] | dq[Mpad] | rowsum[Mpad]
+    const size_t bq_bytes = (size_t)T * Mpad * Kp;
+    const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
+    int rc = ensure_scratch(ctx, bq_al + (size_t)Mpad * 8 + 256);
+    if (rc != FNN_OK) return rc;
+    uint8_t *bq = (uint8_t *)ctx->scratch;
+    float *dq = (float *)(bq + bq_al);
+    float *rowsum = dq + Mpad;
+    if (Mpad > M)  // padded batch rows of every term plane must read as zero
+        FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
+                                         (size_t)(Mpad - M) * Kp, T, ctx->stream),
+                       FNN_ERR_DISPATCH);
+    act_prep_kernel<KIND><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+
+    CUtensorMap map_w, map_a;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        cuuint64_t strides[1] = {(cuuint64_t)w->ld_u4 * 16};
+        cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
+        rc = encode_map(&map_w, w->rows, 2, dims, strides, box);
+        if (rc != FNN_OK) return rc;
+    }
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Mpad, (cuuint64_t)T};
+        cuuint64_t strides[2] = {(cuuint64_t)Kp, (cuuint64_t)Kp * Mpad};
+        cuuint32_t box[3] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)Mb, (cuuint32_t)T};
+        rc = encode_map(&map_a, bq, 3, dims, strides, box);
+        if (rc != FNN_OK) return rc;
+    }
+
+    TcParams p{};
+    p.scales = w->scales;
+    p.zeros = w->zeros;
+    p.bias = a.bias;
+    p.dq = dq;
+    p.rowsum = rowsum;
+    p.out = a.out;
+    p.err_flag = ctx->err_flag;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.Mb = Mb;
+    p.n_tiles = (N + kTileN - 1) / kTileN;
+    p.m_tiles = m_tiles;
+    p.kblocks = (K + kKBlockBytes - 1) / kKBlockBytes;
+    p.epilogue = a.epilogue;
+    const int a_bytes = kTileN * kKBlockBytes;
+    const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
+    int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride));
+    stages = std::max(2, std::min(stages, 8));
+    p.stages = stages;
+    const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride) + (2 * stages + 4) * 8 + 64;
+    const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
+    auto kern = qmm_tc_kernel<KIND>;
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   FNN_ERR_DISPATCH);
+    kern<<<grid, kThreadsTc, smem, ctx->stream>>>(map_w, map_a, p);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    ctx->last_path = "tc";
+    return FNN_OK;
+}
+
+}  // namespace
+
+bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
+    (void)M;
+    // natively supported codes whose rows TMA can address (16-byte row stride is guaranteed by the
+    // row-padded layout); K below one swizzle row gains nothing here
+    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) && w->K >= 128 && w->N >= 1 &&
+           w->N < (1u << 30) && w->K < (1u << 30);
+}
+
+int prepare_qmm_tc(fnn_cuda_ctx *, fnn_cuda_qweight *) { return FNN_OK; }
+
+int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    FNN_REQUIRE(a.M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul: M=%zu too large for the tcgen05 path", a.M);
+    if (a.w->fmt == FNN_FMT_I8) return launch_tc<KIND_I8>(ctx, a);
+    if (a.w->fmt == FNN_FMT_F8) return launch_tc<KIND_F8>(ctx, a);
+    return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
+}
+
 }  // namespace fnn

@@ -388,3 +388,41 @@ def test_mma_kernel_flags_activations_outside_fp16_range(backend):
         backend.synchronize()
     finally:
         rig.close()
+
+
+# ---- tcgen05 / TMEM / TMA kernel (native I8 and FP8 codes) ---------------------------------------------
+
+TC_SHAPES = [(128, 128), (4096, 256), (1000, 200), (512, 1040), (8192, 384)]
+
+
+@pytest.mark.parametrize("fmt", [orc.FMT_I8, orc.FMT_F8])
+@pytest.mark.parametrize("kn", TC_SHAPES)
+def test_tcgen05_kernel_parity(backend, fmt, kn):
+    k, n = kn
+    w = normal(150 + k + n, (k, n), 0.02)
+    bias = normal(160 + n, (n,), 0.01)
+    q = orc.quantize_kn(fmt, w)
+    ms = [1, 5, 16, 100, 128, 300, 512]
+    rig = Rig(backend, q, max(ms))
+    try:
+        for m in ms:
+            x = normal(170 + m, (m, k), 1.0)
+            b, epi = ((bias, L.EPI_GELU) if m % 2 else (None, L.EPI_SILU))
+            got = rig.run(x, b, epi, L.PATH_TC)
+            backend.synchronize()  # a bounded wait that gave up would raise here
+            assert backend.last_path() == "tc"
+            want = orc.qmatmul(q, x, b, epi)
+            err = max_err_vs_rms(got, want)
+            assert err <= TOL_F32, (orc.FMT_NAMES[fmt], kn, m, err)
+    finally:
+        rig.close()
+
+
+def test_tcgen05_path_rejects_formats_it_does_not_cover(backend):
+    q = orc.quantize_kn(orc.FMT_I4, normal(1, (256, 128), 0.02))
+    rig = Rig(backend, q, 1)
+    try:
+        with pytest.raises(fnn.BackendError, match="tcgen05 path does not cover"):
+            rig.run(normal(2, (1, 256), 1.0), None, L.EPI_NONE, L.PATH_TC)
+    finally:
+        rig.close()
