@@ -313,7 +313,8 @@ static int qmatmul_impl(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a, 
     QmmArgs args{w, a, out, bias, M, epilogue};
     switch (path) {
     case FNN_PATH_AUTO:
-        if (qmm_tc_supported(w, M) && M >= 128) return launch_qmm_tc(ctx, args);
+        // measured crossover: the fragment kernel wins up to 8 batch rows, tcgen05 beyond
+        if (qmm_tc_supported(w, M) && M > 8) return launch_qmm_tc(ctx, args);
         // tiny layers stay on the row kernel: a 16-row x 128-k fragment tile would be mostly padding
         if (qmm_mma_supported(w, M) && auto_uses_mma(w)) return launch_qmm_mma(ctx, args);
         return launch_qmm_rows(ctx, args);

@@ -93,6 +93,7 @@ struct fnn_cuda_qweight {
     // tile-major copy for the tcgen05 kernel (built on demand)
     void *tc = nullptr;
     size_t tc_bytes = 0;
+    size_t tc_ld = 0;           // row stride of the byte-expanded copy
     int tc_kind = 0;
 };
 

@@ -150,11 +150,10 @@ __host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols) {
 // ---- activation rewrite ---------------------------------------------------------------------
 // One block per batch row.  Writes T byte planes Bq[t][m][Kp] (rows zero-padded to Kp), the
 // per-row factor dq[m] and the row sum.
-template <int KIND>
+template <int KIND, int T>
 __global__ void __launch_bounds__(256)
 act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
                 float *__restrict__ dq, float *__restrict__ rowsum) {
-    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
     __shared__ float s_max[8], s_sum[8];
     const int m = blockIdx.x, tid = threadIdx.x;
     const float *row = act + (size_t)m * K;
@@ -201,7 +200,7 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
         } else {
             float r = x;
 #pragma unroll
-            for (int i = 0; i < 3; ++i) {
+            for (int i = 0; i < T; ++i) {
                 __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
                 t[i] = (uint8_t)c;
                 r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
@@ -230,11 +229,10 @@ struct TcParams {
     int epilogue;
 };
 
-template <int KIND>
+template <int KIND, int T>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
               TcParams p) {
-    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is what the 128B swizzle atoms need
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -376,8 +374,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     float acc;
                     if (KIND == KIND_I8)
                         acc = (float)(int)r[0][j] * 128.0f + (float)(int)r[1][j];
+                    else if (T == 3)
+                        acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) +
+                              __uint_as_float(r[T - 1][j]);
                     else
-                        acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) + __uint_as_float(r[2][j]);
+                        acc = __uint_as_float(r[0][j]) + __uint_as_float(r[1][j]);
                     const float dot = acc * p.dq[m];
                     const float v = finish_output(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
                                                   p.bias != nullptr, bias, p.epilogue);
@@ -424,14 +425,13 @@ int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, c
     return FNN_OK;
 }
 
-template <int KIND>
+template <int KIND, int T>
 int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
-    constexpr int T = (KIND == KIND_I8) ? 2 : 3;
     const fnn_cuda_qweight *w = a.w;
     const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
     const int Kp = (K + 15) & ~15;  // TMA strides are multiples of 16 bytes
     // batch rows per tile: T*Mb is the MMA N (multiple of 16, at most 256)
-    const int mb_max = (KIND == KIND_I8) ? 128 : 80;
+    const int mb_max = (T == 2) ? 128 : 80;
     int Mb = std::min(mb_max, (M + 15) & ~15);
     const int m_tiles = (M + Mb - 1) / Mb;
     const int Mpad = m_tiles * Mb;
@@ -448,16 +448,18 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
                                          (size_t)(Mpad - M) * Kp, T, ctx->stream),
                        FNN_ERR_DISPATCH);
-    act_prep_kernel<KIND><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
+    act_prep_kernel<KIND, T><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
     FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
     ctx->launches++;
 
     CUtensorMap map_w, map_a;
     {
         cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
-        cuuint64_t strides[1] = {(cuuint64_t)w->ld_u4 * 16};
+        // 8-bit codes are read in place; 4-bit codes from their byte-expanded copy
+        void *base = w->tc ? w->tc : (void *)w->rows;
+        cuuint64_t strides[1] = {w->tc ? (cuuint64_t)w->tc_ld : (cuuint64_t)w->ld_u4 * 16};
         cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
-        rc = encode_map(&map_w, w->rows, 2, dims, strides, box);
+        rc = encode_map(&map_w, base, 2, dims, strides, box);
         if (rc != FNN_OK) return rc;
     }
     {
@@ -491,7 +493,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     p.stages = stages;
     const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride) + (2 * stages + 4) * 8 + 64;
     const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
-    auto kern = qmm_tc_kernel<KIND>;
+    auto kern = qmm_tc_kernel<KIND, T>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
     kern<<<grid, kThreadsTc, smem, ctx->stream>>>(map_w, map_a, p);
@@ -501,22 +503,71 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     return FNN_OK;
 }
 
+
+// 4-bit codes -> one byte per weight, exactly: e2m1 -> the e4m3 code of the same value,
+// two's-complement nibble -> int8.  [N][ld] bytes, ld a multiple of 16.
+__global__ void expand_nibbles_kernel(int fmt, const uint32_t *rows, size_t ld_words, size_t N, size_t K,
+                                      size_t ld, uint8_t *out) {
+    const size_t total = N * ld;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t n = i / ld, k = i % ld;
+        uint8_t v = 0;
+        if (k < K) {
+            const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
+            if (fmt == FNN_FMT_I4) {
+                v = (uint8_t)(int8_t)(((int32_t)(nib << 28)) >> 28);
+            } else {
+                // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 as e4m3 (bias 7, 3 mantissa bits)
+                const uint8_t lut[8] = {0x00, 0x30, 0x38, 0x3C, 0x40, 0x44, 0x48, 0x4C};
+                v = (uint8_t)(lut[nib & 7u] | ((nib & 8u) << 4));
+            }
+        }
+        out[i] = v;
+    }
+}
+
 }  // namespace
 
 bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
     (void)M;
-    // natively supported codes whose rows TMA can address (16-byte row stride is guaranteed by the
-    // row-padded layout); K below one swizzle row gains nothing here
-    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) && w->K >= 128 && w->N >= 1 &&
-           w->N < (1u << 30) && w->K < (1u << 30);
+    // codes the tensor core takes natively (I8, FP8) or after an exact one-byte expansion (I4, FP4);
+    // the codebook format needs per-block scales inside K and stays on the other kernels
+    return w->fmt != FNN_FMT_I4CB && w->K >= 128 && w->N >= 1 && w->N < (1u << 30) &&
+           w->K < (1u << 30);
 }
 
-int prepare_qmm_tc(fnn_cuda_ctx *, fnn_cuda_qweight *) { return FNN_OK; }
+int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
+    if (w->tc || (w->fmt != FNN_FMT_I4 && w->fmt != FNN_FMT_F4)) return FNN_OK;
+    FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
+                "first tcgen05 use of a 4-bit weight happened during graph capture; run the plan once "
+                "before capturing it");
+    const size_t ld = (w->K + 15) & ~(size_t)15;
+    FNN_CUDA_CHECK(cudaMalloc(&w->tc, w->N * ld), FNN_ERR_MEMORY);
+    w->tc_bytes = w->N * ld;
+    w->tc_ld = ld;
+    const int blocks = (int)std::min<size_t>(div_ceil(w->N * ld, 256), (size_t)ctx->sm_count * 16);
+    expand_nibbles_kernel<<<blocks, 256, 0, ctx->stream>>>(w->fmt, (const uint32_t *)w->rows, w->ld_u4 * 4,
+                                                          w->N, w->K, ld, (uint8_t *)w->tc);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    return FNN_OK;
+}
 
 int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     FNN_REQUIRE(a.M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul: M=%zu too large for the tcgen05 path", a.M);
-    if (a.w->fmt == FNN_FMT_I8) return launch_tc<KIND_I8>(ctx, a);
-    if (a.w->fmt == FNN_FMT_F8) return launch_tc<KIND_F8>(ctx, a);
+    int rc = prepare_qmm_tc(ctx, const_cast<fnn_cuda_qweight *>(a.w));
+    if (rc != FNN_OK) return rc;
+    switch (a.w->fmt) {
+    case FNN_FMT_I8:
+    case FNN_FMT_I4:
+        return launch_tc<KIND_I8, 2>(ctx, a);
+    case FNN_FMT_F8:
+    case FNN_FMT_F4:
+        // three e4m3 terms keep f32-grade accuracy while the scan of the weights is the bound;
+        // two terms (~1e-3 of the output norm) once the tensor core is
+        return a.M >= 128 ? launch_tc<KIND_F8, 2>(ctx, a) : launch_tc<KIND_F8, 3>(ctx, a);
+    }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
 }
 
