@@ -251,13 +251,14 @@ def sweep_points(L):
         ("c2_i8", L.FMT_I8, 4096, 11008, (1, 16, 128, 512), 0.02, L.EPI_SILU, False),
         ("c1_i4", L.FMT_I4, 4096, 4096, (1, 8), 0.02, L.EPI_NONE, True),
         ("c3_i4", L.FMT_I4, 8192, 28672, (1,), 0.015, L.EPI_NONE, False),
-        ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
-        ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512), 0.015, L.EPI_NONE, False),
+        ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
+        ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
         ("c4_i4cb_up", L.FMT_I4CB, 2048, 8192, (1, 64), 0.02, L.EPI_GELU, True),
+        ("c5_i4_gateup", L.FMT_I4, 4096, 28672, (64,), 0.02, L.EPI_NONE, False),
     ]
 
 
-def run_sweep(fnn, backend, peaks, budget_s=150.0, only=None, only_m=None, steps_override=None,
+def run_sweep(fnn, backend, peaks, budget_s=240.0, only=None, only_m=None, steps_override=None,
               path=0):
     from fastnn_b200 import _lib as L
     out, t_start = [], time.time()
@@ -397,9 +398,10 @@ def run_ours(args):
     backend.close()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
-# ncu capture summarised under profiles/ (None until a capture has been taken).
-NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel
+# (qmm_mma_kernel, I8, K=4096, N=11008, M=1), from the ncu capture summarised in
+# profiles/qmm_mma_i8_m1_config2.md: 45.228 MB read + 2.6 KB written.
+NCU_TRAFFIC_BYTES = 45230848
 
 
 def time_sharded(torch, dist, backend, layer, args, world, L):

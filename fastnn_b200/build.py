@@ -68,7 +68,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         logs = list(pool.map(lambda c: _run(c, verbose), jobs))
     with open(os.path.join(OBJ, "ptxas.log"), "w") as f:
         f.write("\n".join(logs))
-    _run([NVCC, "-shared", "-ccbin", HOST_CXX, "-o", LIB, *objs, "-lcuda", "-Xcompiler", "-fopenmp",
+    _run([NVCC, "-shared", "-ccbin", HOST_CXX, "-o", LIB, *objs, "-Xcompiler", "-fopenmp",
           "-lgomp"], verbose)
     return LIB
 

@@ -33,7 +33,7 @@ constexpr int kKBlockBytes = 128;  // bytes of K per pipeline stage = one 128B s
 constexpr int kThreadsTc = 192;
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any legitimate wait
 
-enum { KIND_I8 = 0, KIND_F8 = 1 };
+enum { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 
@@ -108,10 +108,16 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
             "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
-    } else {
+    } else if (KIND == KIND_F8) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
             ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
     }
@@ -143,7 +149,7 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor: D format, A/B formats, K-major both, N (>>3) and M (>>4).
 __host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols) {
     return (kind == KIND_I8 ? (2u << 4) | (1u << 7) | (1u << 10)   // S32 accum, signed 8-bit A and B
-                            : (1u << 4) | (0u << 7) | (0u << 10))  // F32 accum, E4M3 A and B
+                            : (1u << 4) | (0u << 7) | (0u << 10))  // F32 accum; format 0 = E4M3 (f8f6f4) or F16 (f16)
            | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
 }
 
@@ -181,6 +187,16 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
         sum += s_sum[w];
     }
     const float full = (KIND == KIND_I8) ? 16256.0f : 448.0f;
+    if (KIND == KIND_F16) {
+        // one fp16 term, no rescaling: bq is [Mpad][Kp bytes] of halves
+        if (tid == 0) {
+            dq[m] = 1.0f;
+            rowsum[m] = sum;
+        }
+        __half *dst = reinterpret_cast<__half *>(bq + (size_t)m * Kp);
+        for (int k = tid; k < Kp / 2; k += 256) dst[k] = __float2half_rn(k < K ? row[k] : 0.0f);
+        return;
+    }
     const float step = (mx > 0.0f && isfinite(mx)) ? mx / full : 1.0f;
     const float inv = 1.0f / step;
     if (tid == 0) {
@@ -358,7 +374,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             tc_fence_after();
             const int n = nt * kTileN + quad * 32 + lane;
             const bool n_ok = n < p.N;
-            const float scale = n_ok ? p.scales[n] : 0.0f;
+            const float scale = n_ok ? (p.scales ? p.scales[n] : 1.0f) : 0.0f;
             const float zero = (n_ok && has_zero) ? p.zeros[n] : 0.0f;
             const float bias = (n_ok && p.bias) ? p.bias[n] : 0.0f;
             const uint32_t t_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BNt);
@@ -372,13 +388,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     const int m = mt * p.Mb + c0 + j;
                     if (m >= p.M || c0 + j >= p.Mb) continue;
                     float acc;
-                    if (KIND == KIND_I8)
+                    if (T == 1)
+                        acc = __uint_as_float(r[0][j]);
+                    else if (KIND == KIND_I8)
                         acc = (float)(int)r[0][j] * 128.0f + (float)(int)r[1][j];
                     else if (T == 3)
                         acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) +
                               __uint_as_float(r[T - 1][j]);
                     else
-                        acc = __uint_as_float(r[0][j]) + __uint_as_float(r[1][j]);
+                        acc = __uint_as_float(r[0][j]) + __uint_as_float(r[T > 1 ? 1 : 0][j]);
                     const float dot = acc * p.dq[m];
                     const float v = finish_output(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
                                                   p.bias != nullptr, bias, p.epilogue);
@@ -410,28 +428,43 @@ struct TcWeightMaps {
     CUtensorMap w;
 };
 
+// cuTensorMapEncodeTiled is looked up through the runtime, so the library itself carries no
+// link-time dependency on libcuda (it must load, and fail cleanly, on a machine without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
 int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
                const cuuint32_t *box) {
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims,
-                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        const char *msg = nullptr;
-        cuGetErrorString(r, &msg);
-        return set_error(FNN_ERR_DISPATCH, "cuTensorMapEncodeTiled failed: %s", msg ? msg : "?");
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        FNN_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres),
+                       FNN_ERR_UNSUPPORTED);
+        FNN_REQUIRE(fn != nullptr && qres == cudaDriverEntryPointSuccess, FNN_ERR_UNSUPPORTED,
+                    "the CUDA driver does not provide cuTensorMapEncodeTiled");
+        encode = (EncodeTiledFn)fn;
     }
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(FNN_ERR_DISPATCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return FNN_OK;
 }
 
 template <int KIND, int T>
 int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const fnn_cuda_qweight *w = a.w;
+    constexpr int ES = (KIND == KIND_F16) ? 2 : 1;  // bytes per operand element
     const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
-    const int Kp = (K + 15) & ~15;  // TMA strides are multiples of 16 bytes
+    const int Kbytes = K * ES;
+    const int Kp = (Kbytes + 15) & ~15;  // row bytes; TMA strides are multiples of 16 bytes
     // batch rows per tile: T*Mb is the MMA N (multiple of 16, at most 256)
-    const int mb_max = (T == 2) ? 128 : 80;
+    const int mb_max = (T == 1) ? 256 : (T == 2) ? 128 : 80;
     int Mb = std::min(mb_max, (M + 15) & ~15);
     const int m_tiles = (M + Mb - 1) / Mb;
     const int Mpad = m_tiles * Mb;
@@ -454,7 +487,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 
     CUtensorMap map_w, map_a;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        cuuint64_t dims[2] = {(cuuint64_t)Kbytes, (cuuint64_t)N};
         // 8-bit codes are read in place; 4-bit codes from their byte-expanded copy
         void *base = w->tc ? w->tc : (void *)w->rows;
         cuuint64_t strides[1] = {w->tc ? (cuuint64_t)w->tc_ld : (cuuint64_t)w->ld_u4 * 16};
@@ -471,7 +504,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     }
 
     TcParams p{};
-    p.scales = w->scales;
+    p.scales = (w->fmt == FNN_FMT_I4CB) ? nullptr : w->scales;  // block scales are folded into the copy
     p.zeros = w->zeros;
     p.bias = a.bias;
     p.dq = dq;
@@ -484,7 +517,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     p.Mb = Mb;
     p.n_tiles = (N + kTileN - 1) / kTileN;
     p.m_tiles = m_tiles;
-    p.kblocks = (K + kKBlockBytes - 1) / kKBlockBytes;
+    p.kblocks = (Kbytes + kKBlockBytes - 1) / kKBlockBytes;
     p.epilogue = a.epilogue;
     const int a_bytes = kTileN * kKBlockBytes;
     const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
@@ -503,6 +536,23 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     return FNN_OK;
 }
 
+
+// Codebook weights -> fp16 of blockscale * centroid (one rounding), [N][ld bytes], for kind::f16.
+__global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
+                                       const float *bscales, size_t bpr, const float *codebook, size_t ld,
+                                       __half *out) {
+    const size_t ldh = ld / 2, total = N * ldh;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t n = i / ldh, k = i % ldh;
+        float v = 0.0f;
+        if (k < K) {
+            const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
+            v = __fmul_rn(bscales[n * bpr + k / kCodebookBlock], codebook[nib]);
+        }
+        out[i] = __float2half_rn(v);
+    }
+}
 
 // 4-bit codes -> one byte per weight, exactly: e2m1 -> the e4m3 code of the same value,
 // two's-complement nibble -> int8.  [N][ld] bytes, ld a multiple of 16.
@@ -531,17 +581,31 @@ __global__ void expand_nibbles_kernel(int fmt, const uint32_t *rows, size_t ld_w
 
 bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
     (void)M;
-    // codes the tensor core takes natively (I8, FP8) or after an exact one-byte expansion (I4, FP4);
-    // the codebook format needs per-block scales inside K and stays on the other kernels
-    return w->fmt != FNN_FMT_I4CB && w->K >= 128 && w->N >= 1 && w->N < (1u << 30) &&
-           w->K < (1u << 30);
+    // codes the tensor core takes natively (I8, FP8), after an exact one-byte expansion (I4, FP4),
+    // or -- the codebook format, whose block scales vary inside K -- as an fp16 copy of
+    // blockscale * centroid (only when those stay inside the fp16 range)
+    if (w->fmt == FNN_FMT_I4CB && !w->mma_ok) return false;
+    return w->K >= 128 && w->N >= 1 && w->N < (1u << 30) && w->K < (1u << 29);
 }
 
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
-    if (w->tc || (w->fmt != FNN_FMT_I4 && w->fmt != FNN_FMT_F4)) return FNN_OK;
+    if (w->tc || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) return FNN_OK;
     FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
                 "first tcgen05 use of a 4-bit weight happened during graph capture; run the plan once "
                 "before capturing it");
+    if (w->fmt == FNN_FMT_I4CB) {
+        const size_t ldb = (w->K * 2 + 15) & ~(size_t)15;
+        FNN_CUDA_CHECK(cudaMalloc(&w->tc, w->N * ldb), FNN_ERR_MEMORY);
+        w->tc_bytes = w->N * ldb;
+        w->tc_ld = ldb;
+        const int nb = (int)std::min<size_t>(div_ceil(w->N * ldb / 2, 256), (size_t)ctx->sm_count * 16);
+        expand_codebook_kernel<<<nb, 256, 0, ctx->stream>>>((const uint32_t *)w->rows, w->ld_u4 * 4, w->N,
+                                                          w->K, w->scales, w->blocks_per_row, w->codebook,
+                                                          ldb, (__half *)w->tc);
+        FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+        ctx->launches++;
+        return FNN_OK;
+    }
     const size_t ld = (w->K + 15) & ~(size_t)15;
     FNN_CUDA_CHECK(cudaMalloc(&w->tc, w->N * ld), FNN_ERR_MEMORY);
     w->tc_bytes = w->N * ld;
@@ -567,6 +631,8 @@ int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         // three e4m3 terms keep f32-grade accuracy while the scan of the weights is the bound;
         // two terms (~1e-3 of the output norm) once the tensor core is
         return a.M >= 128 ? launch_tc<KIND_F8, 2>(ctx, a) : launch_tc<KIND_F8, 3>(ctx, a);
+    case FNN_FMT_I4CB:
+        return launch_tc<KIND_F16, 1>(ctx, a);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
 }

@@ -395,7 +395,7 @@ def test_mma_kernel_flags_activations_outside_fp16_range(backend):
 TC_SHAPES = [(128, 128), (4096, 256), (1000, 200), (512, 1040), (8192, 384)]
 
 
-@pytest.mark.parametrize("fmt", [orc.FMT_I8, orc.FMT_F8, orc.FMT_I4, orc.FMT_F4])
+@pytest.mark.parametrize("fmt", [orc.FMT_I8, orc.FMT_F8, orc.FMT_I4, orc.FMT_F4, orc.FMT_I4CB])
 @pytest.mark.parametrize("kn", TC_SHAPES)
 def test_tcgen05_kernel_parity(backend, fmt, kn):
     k, n = kn
@@ -415,17 +415,19 @@ def test_tcgen05_kernel_parity(backend, fmt, kn):
             err = max_err_vs_rms(got, want)
             # int8 pairs and e4m3 triples of the activations are f32-grade; from 128 batch rows
             # on the e4m3 formats use two terms (tensor-core tolerance)
-            tol = TOL_TC if (m >= 128 and fmt in (orc.FMT_F8, orc.FMT_F4)) else TOL_F32
+            # (the codebook format runs on an fp16 copy with one fp16 activation term)
+            tol = TOL_TC if ((m >= 128 and fmt in (orc.FMT_F8, orc.FMT_F4)) or fmt == orc.FMT_I4CB) \
+                else TOL_F32
             assert err <= tol, (orc.FMT_NAMES[fmt], kn, m, err)
     finally:
         rig.close()
 
 
-def test_tcgen05_path_rejects_formats_it_does_not_cover(backend):
-    q = orc.quantize_kn(orc.FMT_I4CB, normal(1, (256, 128), 0.02))
+def test_tcgen05_path_rejects_shapes_it_does_not_cover(backend):
+    q = orc.quantize_kn(orc.FMT_I8, normal(1, (64, 128), 0.02))   # K below one 128-byte swizzle row
     rig = Rig(backend, q, 1)
     try:
         with pytest.raises(fnn.BackendError, match="tcgen05 path does not cover"):
-            rig.run(normal(2, (1, 256), 1.0), None, L.EPI_NONE, L.PATH_TC)
+            rig.run(normal(2, (1, 64), 1.0), None, L.EPI_NONE, L.PATH_TC)
     finally:
         rig.close()
