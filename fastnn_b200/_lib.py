@@ -52,6 +52,7 @@ SIGNATURES = {
     "fnn_cuda_qweight_dequant": (_int, [_vp, _vp, _sz]),
     "fnn_cuda_qmatmul": (_int, [_vp, _vp, _vp, _sz, _sz, _i64, _sz, _int, _int]),
     "fnn_cuda_qmatmul_ptr": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _int, _int]),
+    "fnn_cuda_qmatmul_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _int]),
     "fnn_cuda_last_path": (_c.c_char_p, [_vp]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_memcpy": (_int, [_vp, _vp, _sz, _sz, _sz]),

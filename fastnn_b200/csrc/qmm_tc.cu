@@ -537,6 +537,90 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 }
 
 
+// Same launch sequence over caller-supplied scratch: used by the entry point that may not allocate.
+template <int KIND, int T>
+int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size_t scratch_bytes) {
+    const fnn_cuda_qweight *w = a.w;
+    const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
+    const int Kp = (K + 15) & ~15;  // TMA strides are multiples of 16 bytes
+    // batch rows per tile: T*Mb is the MMA N (multiple of 16, at most 256)
+    const int mb_max = (T == 2) ? 128 : 80;
+    int Mb = std::min(mb_max, (M + 15) & ~15);
+    const int m_tiles = (M + Mb - 1) / Mb;
+    const int Mpad = m_tiles * Mb;
+
+    // scratch: Bq[T][Mpad][Kp] | dq[Mpad] | rowsum[Mpad]
+    const size_t bq_bytes = (size_t)T * Mpad * Kp;
+    const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
+    int rc = FNN_OK;
+    const size_t need = bq_al + (size_t)Mpad * 8 + 256;
+    FNN_REQUIRE(need <= scratch_bytes, FNN_ERR_MEMORY,
+                "qmatmul_noalloc: M=%d, K=%d needs %zu bytes of activation scratch; the built-in "
+                "scratch holds %zu (use fnn_cuda_qmatmul for larger problems)",
+                M, K, need, scratch_bytes);
+    uint8_t *bq = scratch;
+    float *dq = (float *)(bq + bq_al);
+    float *rowsum = dq + Mpad;
+    if (Mpad > M)  // padded batch rows of every term plane must read as zero
+        FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
+                                         (size_t)(Mpad - M) * Kp, T, ctx->stream),
+                       FNN_ERR_DISPATCH);
+    act_prep_kernel<KIND, T><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+
+    CUtensorMap map_w, map_a;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        // 8-bit codes are read in place; 4-bit codes from their byte-expanded copy
+        void *base = w->tc ? w->tc : (void *)w->rows;
+        cuuint64_t strides[1] = {w->tc ? (cuuint64_t)w->tc_ld : (cuuint64_t)w->ld_u4 * 16};
+        cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
+        rc = encode_map(&map_w, base, 2, dims, strides, box);
+        if (rc != FNN_OK) return rc;
+    }
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Mpad, (cuuint64_t)T};
+        cuuint64_t strides[2] = {(cuuint64_t)Kp, (cuuint64_t)Kp * Mpad};
+        cuuint32_t box[3] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)Mb, (cuuint32_t)T};
+        rc = encode_map(&map_a, bq, 3, dims, strides, box);
+        if (rc != FNN_OK) return rc;
+    }
+
+    TcParams p{};
+    p.scales = w->scales;
+    p.zeros = w->zeros;
+    p.bias = a.bias;
+    p.dq = dq;
+    p.rowsum = rowsum;
+    p.out = a.out;
+    p.err_flag = ctx->err_flag;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.Mb = Mb;
+    p.n_tiles = (N + kTileN - 1) / kTileN;
+    p.m_tiles = m_tiles;
+    p.kblocks = (K + kKBlockBytes - 1) / kKBlockBytes;
+    p.epilogue = a.epilogue;
+    const int a_bytes = kTileN * kKBlockBytes;
+    const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
+    int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride));
+    stages = std::max(2, std::min(stages, 8));
+    p.stages = stages;
+    const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride) + (2 * stages + 4) * 8 + 64;
+    const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
+    auto kern = qmm_tc_kernel<KIND, T>;
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   FNN_ERR_DISPATCH);
+    kern<<<grid, kThreadsTc, smem, ctx->stream>>>(map_w, map_a, p);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    ctx->last_path = "tc-noalloc";
+    return FNN_OK;
+}
+
+
 // Codebook weights -> fp16 of blockscale * centroid (one rounding), [N][ld bytes], for kind::f16.
 __global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
                                        const float *bscales, size_t bpr, const float *codebook, size_t ld,
@@ -638,3 +722,58 @@ int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 }
 
 }  // namespace fnn
+
+// ---- entry point that allocates nothing ---------------------------------------------------------
+
+namespace {
+// Activation scratch of fnn_cuda_qmatmul_noalloc.  Lives in the module image: every GPU that
+// loads the library holds these 8 MiB until the process exits.
+constexpr size_t kNoAllocScratchBytes = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+// In host code the symbol above is only a stand-in; the device address is looked up once per
+// device (with that device current) and kept here.
+static void *g_noalloc_scratch_addr[64] = {};
+}  // namespace
+
+extern "C" int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
+                                        float *out_dev, const float *bias_dev, size_t M, int epilogue) {
+    using namespace fnn;
+    clear_error();
+    FNN_REQUIRE(ctx && w && a_dev && out_dev, FNN_ERR_DISPATCH, "qmatmul_noalloc: null argument");
+    FNN_REQUIRE(w->ctx->device == ctx->device, FNN_ERR_DISPATCH,
+                "qmatmul_noalloc: weight lives on device %d, context on %d", w->ctx->device, ctx->device);
+    FNN_REQUIRE(ctx->device >= 0 && ctx->device < 64, FNN_ERR_UNSUPPORTED,
+                "qmatmul_noalloc: device index %d out of range", ctx->device);
+    FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
+                "qmatmul_noalloc: unknown epilogue %d", epilogue);
+    FNN_REQUIRE(((uintptr_t)a_dev & 15u) == 0 && ((uintptr_t)out_dev & 15u) == 0, FNN_ERR_DISPATCH,
+                "qmatmul_noalloc: pointers must be 16-byte aligned");
+    FNN_REQUIRE(qmm_tc_supported(w, M) && w->fmt != FNN_FMT_I4CB, FNN_ERR_UNSUPPORTED,
+                "qmatmul_noalloc: format %d / K=%zu is not served by this entry point", w->fmt, w->K);
+    // 4-bit formats read a byte-expanded copy that fnn_cuda_qweight_prepare(.., FNN_PATH_TC)
+    // builds; building it here would allocate
+    FNN_REQUIRE(w->tc != nullptr || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8, FNN_ERR_MEMORY,
+                "qmatmul_noalloc: call fnn_cuda_qweight_prepare(ctx, w, FNN_PATH_TC) once for 4-bit "
+                "weights before using the entry point that may not allocate");
+    FNN_REQUIRE(M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul_noalloc: M=%zu too large", M);
+    if (M == 0) return FNN_OK;
+    FNN_CUDA_CHECK(cudaSetDevice(ctx->device), FNN_ERR_DISPATCH);
+    if (!g_noalloc_scratch_addr[ctx->device]) {
+        void *ptr = nullptr;
+        FNN_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch), FNN_ERR_MEMORY);
+        FNN_REQUIRE(ptr != nullptr, FNN_ERR_MEMORY, "qmatmul_noalloc: scratch symbol has no address");
+        g_noalloc_scratch_addr[ctx->device] = ptr;
+    }
+    uint8_t *scratch = (uint8_t *)g_noalloc_scratch_addr[ctx->device];
+    QmmArgs args{w, a_dev, out_dev, bias_dev, M, epilogue};
+    switch (w->fmt) {
+    case FNN_FMT_I8:
+    case FNN_FMT_I4:
+        return launch_tc_static<KIND_I8, 2>(ctx, args, scratch, kNoAllocScratchBytes);
+    case FNN_FMT_F8:
+    case FNN_FMT_F4:
+        return M >= 128 ? launch_tc_static<KIND_F8, 2>(ctx, args, scratch, kNoAllocScratchBytes)
+                        : launch_tc_static<KIND_F8, 3>(ctx, args, scratch, kNoAllocScratchBytes);
+    }
+    return set_error(FNN_ERR_UNSUPPORTED, "qmatmul_noalloc: format %d", w->fmt);
+}

@@ -156,6 +156,25 @@ int fnn_cuda_qmatmul(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, fnn_cuda_arena *are
 int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
                          float *out_dev, const float *bias_dev, size_t M, int epilogue,
                          int path);
+/* The same quantized MatMul for callers that must not trigger a device allocation -- no
+ * counterpart in the reference, which runs on host memory only.  Some hosts hand every byte
+ * of device memory to an allocator of their own, or run a latency-critical loop in which
+ * cudaMalloc/cudaFree (which can synchronize the whole device) are off limits; fnn_cuda_qmatmul
+ * may grow the context's scratch buffer on a larger problem, this entry point never calls
+ * cudaMalloc, cudaFree or any allocating routine.  It runs the tcgen05 kernel with the rewritten
+ * activations placed in an 8 MiB scratch array that is part of the library image (every GPU
+ * that loads the library holds it until the process exits).  The rewritten activations must
+ * fit in it: about T * M * K bytes with M and K rounded up to the kernel's tiles (T = 2 byte
+ * planes; 3 for FP8/FP4 below 128 batch rows) -- for example M = 512 at K = 4096, or M = 256 at
+ * K = 8192.  A larger problem is refused with FNN_ERR_MEMORY and both sizes in the message.
+ * a_dev [M,K], out_dev [M,N], bias_dev [N] or NULL are device pointers owned by the caller.
+ * 4-bit weights need one earlier fnn_cuda_qweight_prepare(ctx, w, FNN_PATH_TC); the codebook
+ * format is not served.  The first call on a device looks up the scratch array's device
+ * address; make that call before any stream capture.  All calls share the array and it keeps
+ * the previous call's contents (the kernel clears what has to start at zero itself), so two
+ * calls that overlap on the GPU -- different streams or contexts of one device -- race. */
+int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
+                             float *out_dev, const float *bias_dev, size_t M, int epilogue);
 /* Name of the kernel family the last fnn_cuda_qmatmul on `ctx` launched. */
 const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx);
 
