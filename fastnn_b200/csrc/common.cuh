@@ -183,6 +183,8 @@ int launch_qmm_rows(fnn_cuda_ctx *ctx, const QmmArgs &args);
 bool qmm_mma_supported(const fnn_cuda_qweight *w, size_t M);
 int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &args);
 int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
+bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M);
+int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &args);
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 // shapes automatic dispatch sends to the skinny tensor-core kernel
 static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->mma_ok && w->K >= 512 && w->N >= 64; }

@@ -276,31 +276,38 @@ qmm_mma_kernel(MmaParams p) {
         const int kb0 = k0 / KBLK;
         const int nch = (KBc + kU - 1) / kU;
         const int cpw = (nch + kW - 1) / kW;   // chunks per warp per tile
-        const int nitems = tiles_here * cpw;
 
-        // issue the async copies of item `it` into ring stage it % S (an empty group past the end)
-        auto issue = [&](int it) {
-            const int tl = it / cpw;
-            const int ch = gw + (it - tl * cpw) * kW;
-            const int st = it % S;
+        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
+        // (an empty group once the warp's items are exhausted)
+        int i_tl = 0, i_j = 0, i_st = 0;
+        auto issue_next = [&]() {
+            const bool valid = i_tl < tiles_here;
+            const int ch = gw + i_j * kW;
+            const size_t tile_unit = ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
                 const int kb = ch * kU + u;
-                const bool ok = (it < nitems) && (ch < nch) && (kb < KBc);
+                const bool ok = valid && (kb < KBc);
+                const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const size_t idx =
-                        ok ? (((size_t)(gg + tl * GG) * p.KB + kb0 + kb) * 2 + h) * 32 + lane : 0;
-                    cp_async16(my_ring + (size_t)(st * UNITS + u * 2 + h) * 512, p.frag + idx, ok ? 16 : 0);
+                    cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
+                               ok ? 16 : 0);
                     if (FMT == FNN_FMT_I4CB)
-                        cp_async4(my_ring_bs + (st * UNITS + u * 2 + h) * 32, p.frag_bs + idx, ok ? 4 : 0);
+                        cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
+                                  ok ? 4 : 0);
                 }
             }
             cp_async_commit();
+            if (++i_j == cpw) {
+                i_j = 0;
+                ++i_tl;
+            }
+            if (++i_st == S) i_st = 0;
         };
         // the first weights are in flight while the activations are being staged
 #pragma unroll
-        for (int i = 0; i < S - 1; ++i) issue(i);
+        for (int i = 0; i < S - 1; ++i) issue_next();
 
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
         // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------
@@ -370,18 +377,19 @@ qmm_mma_kernel(MmaParams p) {
         }
 
         // ---- stream this K range of every tile of the group -------------------------------
-        for (int it = 0; it < nitems; ++it) {
-            issue(it + S - 1);
-            cp_async_wait<S - 1>();  // item `it` has landed in this lane's ring
-            const int tl = it / cpw;
-            const int ch = gw + (it - tl * cpw) * kW;
+        int c_st = 0;
+        for (int tl = 0; tl < tiles_here; ++tl)
+        for (int j = 0; j < cpw; ++j) {
+            issue_next();
+            cp_async_wait<S - 1>();  // the current item has landed in this lane's ring
+            const int ch = gw + j * kW;
             uint4 cur[kU][2];
             float cur_bs[kU][2];
 #pragma unroll
             for (int u = 0; u < kU; ++u)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int slot = (it % S) * UNITS + u * 2 + h;
+                    const int slot = c_st * UNITS + u * 2 + h;
                     cur[u][h] = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
                     cur_bs[u][h] = (FMT == FNN_FMT_I4CB) ? my_ring_bs[slot * 32] : 0.0f;
                 }
@@ -430,7 +438,8 @@ qmm_mma_kernel(MmaParams p) {
                 }
             }
             // last chunk of a tile: reduce the group's partial tiles in a fixed order
-            if (it - tl * cpw == cpw - 1) {
+            if (++c_st == S) c_st = 0;
+            if (j == cpw - 1) {
                 float *red = my_red + (size_t)red_buf * kW * CG * 128;
 #pragma unroll
                 for (int cg = 0; cg < CG; ++cg)
@@ -575,28 +584,29 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
     const size_t ring = (size_t)G * kW * stages_for(CG) * kU * 2 * (512 + (FMT == FNN_FMT_I4CB ? 128 : 0));
     const size_t fixed = ring + (size_t)(G * 2 * kW * CG * 128 + G * kW * 64 + 64) * 4 + lut;
     const size_t per_tile = (size_t)G * (CG * 512 + 192);  // output accumulator + row metadata
-    const size_t out_budget = 12 * 1024;
     const size_t cap = 226 * 1024;
+    // one block per SM whenever the per-group accumulators of ceil(tiles / groups) tiles fit next to
+    // at least one ring chunk of activations; otherwise more blocks, run in waves
     const size_t min_act = (size_t)act_rows * (2 * T::KBLK * kU + T::PAD_BYTES);
-    FNN_REQUIRE(fixed + out_budget + min_act <= cap, FNN_ERR_UNSUPPORTED,
+    FNN_REQUIRE(fixed + per_tile + min_act <= cap, FNN_ERR_UNSUPPORTED,
                 "qmatmul: shared memory budget exceeded for M=%d on the skinny tensor-core path", M);
-    const size_t act_budget = cap - fixed - out_budget;
-    int Kc = Kpad;
-    while ((size_t)act_rows * (2 * Kc + T::PAD_BYTES) > act_budget && Kc > T::KBLK * kU) {
-        Kc = (Kc / 2 + T::KBLK - 1) / T::KBLK * T::KBLK;
-    }
-    p.Kc = Kc;
-    const size_t act_bytes = (size_t)act_rows * (2 * Kc + T::PAD_BYTES);
-    const int tpg_max = (int)std::max<size_t>(1, out_budget / per_tile);
     int grid = ctx->sm_count;
     int tpg = (int)div_ceil((size_t)p.ntiles, (size_t)grid * G);
-    if (tpg > tpg_max) {  // very tall layers: more blocks than SMs, run in waves
+    const int tpg_max = (int)((cap - fixed - min_act) / per_tile);
+    if (tpg > tpg_max) {
         tpg = tpg_max;
         grid = (int)div_ceil((size_t)p.ntiles, (size_t)G * tpg);
     }
     if (tpg < 1) tpg = 1;
     grid = (int)std::min<size_t>((size_t)grid, div_ceil((size_t)p.ntiles, (size_t)G));
     p.tiles_per_group = tpg;
+    const size_t act_budget = cap - fixed - (size_t)tpg * per_tile;
+    int Kc = Kpad;
+    while ((size_t)act_rows * (2 * Kc + T::PAD_BYTES) > act_budget && Kc > T::KBLK * kU) {
+        Kc = (Kc / 2 + T::KBLK - 1) / T::KBLK * T::KBLK;
+    }
+    p.Kc = Kc;
+    const size_t act_bytes = (size_t)act_rows * (2 * Kc + T::PAD_BYTES);
     const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
     auto kern = qmm_mma_kernel<FMT, CG>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
@@ -644,6 +654,9 @@ int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) { return ensure_frag
 int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     int rc = ensure_frag(ctx, const_cast<fnn_cuda_qweight *>(a.w));
     if (rc != FNN_OK) return rc;
+    // up to 8 batch rows the 8-bit operand kernel reads the same fragment layout with far fewer
+    // instructions per weight; the fp16 kernel below serves the codebook format and larger batches
+    if (qmm_mma8_supported(a.w, a.M)) return launch_qmm_mma8(ctx, a);
     switch (a.w->fmt) {
     case FNN_FMT_I8:
         return launch_mma_fmt<FNN_FMT_I8>(ctx, a);

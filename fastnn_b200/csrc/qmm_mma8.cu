@@ -1,0 +1,491 @@
+// Skinny-M kernel (1 <= M <= 8) on 8-bit tensor-core operands: the HBM scan of the weights with
+// almost no instruction per weight.
+//
+// Same skeleton as the fp16 fragment kernel (fragment-major weights, one block per SM, groups of
+// eight warps that split K, a private cp.async ring per lane), but the codes are fed to
+// `mma.sync.m16n8k32` as 8-bit operands:
+//   I8   -> s8 operands as stored (no decode at all)
+//   I4   -> s8 operands holding 16*q: two masks per word of eight codes
+//   FP8  -> e4m3 operands as stored
+//   FP4  -> e4m3 codes of the same values through a byte-permute table
+// and the f32 activations are rewritten while they are staged, per batch row, as
+//   int8:  a ~= dq * (128*hi + lo)        (15-bit fixed point, exact int32 accumulation)
+//   e4m3:  a ~= dq * (t1 + t2 [+ t3])     (three terms up to 2 batch rows, two beyond)
+// Partial sums of the int formats are integers, so the split-K reduction is exact in any order.
+// Epilogue as everywhere:  out = act(dq*acc*scale[n] + zero[n]*sum_k a[m,k] + bias[n])
+// (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
+#include "common.cuh"
+
+#include <algorithm>
+#include <cuda_fp8.h>
+
+namespace fnn {
+
+namespace {
+
+constexpr int kW8 = 8;   // warps per group
+constexpr int kU8 = 2;   // k-blocks per ring chunk
+constexpr int kS8 = 3;   // ring stages per lane (two chunks, 96 KB per SM, in flight)
+constexpr int kG8 = 3;   // groups per block
+
+template <int FMT>
+struct T8 {
+    static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4);
+    static constexpr bool is_int = (FMT == FNN_FMT_I8 || FMT == FNN_FMT_I4);
+    static constexpr int KBLK = four_bit ? 128 : 64;       // k per k-block (4 lanes x 16 bytes per row)
+    static constexpr int MMAS = four_bit ? 4 : 2;          // m16n8k32 MMAs per k-block
+    static constexpr int PAD = four_bit ? 16 : 64;         // activation row padding (bank spread)
+};
+
+__device__ __forceinline__ void group_barrier8(int group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kW8 * 32) : "memory");
+}
+__device__ __forceinline__ void cp16(void *dst, const void *src, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void mma_s8(int *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_e4m3(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// prmt.b32 in its default mode: selector nibble n picks byte n&7 of {a, b}; bit 3 of the nibble
+// replaces the byte by its sign bit replicated eight times.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Eight 4-bit codes of one word -> the two A registers of one m16n8k32 MMA.
+//   I4: lo = 16*q of codes 0,2,4,6 ; hi = 16*q of codes 1,3,5,7 (the activations are staged in the
+//       matching order 0,2,4,6,1,3,5,7 of each 8-group)
+//   F4: lo = e4m3 codes of elements 0..3, hi = of elements 4..7 (natural order)
+template <int FMT>
+__device__ __forceinline__ void decode4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    if (FMT == FNN_FMT_I4) {
+        lo = (w << 4) & 0xF0F0F0F0u;
+        hi = w & 0xF0F0F0F0u;
+    } else {
+        // magnitudes 0,.5,1,1.5 | 2,3,4,6 as e4m3; a selector nibble is the 3-bit magnitude code
+        const uint32_t lutA = 0x3C383000u, lutB = 0x4C484440u;
+        const uint32_t mlo = prmt(lutA, lutB, w & 0x7777u);
+        const uint32_t mhi = prmt(lutA, lutB, (w >> 16) & 0x7777u);
+        // sign bytes: the top bit of each byte of (w << 4) / w is the sign of an even / odd code;
+        // selector nibble | 8 replicates that bit across the byte
+        const uint32_t sh = w << 4;
+        const uint32_t slo = prmt(sh, w, 0xD9C8u);  // codes 0,1,2,3 <- sh.b0, w.b0, sh.b1, w.b1
+        const uint32_t shi = prmt(sh, w, 0xFBEAu);  // codes 4,5,6,7 <- sh.b2, w.b2, sh.b3, w.b3
+        lo = mlo | (slo & 0x80808080u);
+        hi = mhi | (shi & 0x80808080u);
+    }
+}
+
+// Staged byte position of activation k inside its row.
+template <int FMT>
+__device__ __forceinline__ int act_pos8(int k) {
+    if (FMT == FNN_FMT_I4) {
+        const int i = k & 7;
+        return (k & ~7) | ((i >> 1) + (i & 1) * 4);  // 0,2,4,6,1,3,5,7
+    }
+    return k;
+}
+
+struct P8 {
+    const uint4 *frag;
+    const float *scales;
+    const float *zeros;
+    const float *act;
+    float *out;
+    const float *bias;
+    int M, N, K;
+    int KB, ntiles, tiles_per_group;
+    int Kc;      // activations staged per pass (multiple of KBLK)
+    int T;       // activation terms (2 for int8; 3 or 2 for e4m3)
+    int epilogue;
+};
+
+template <int FMT, int CG>
+__global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
+qmm_mma8_kernel(P8 p) {
+    using TT = T8<FMT>;
+    constexpr int KBLK = TT::KBLK, MMAS = TT::MMAS;
+    constexpr bool INT = TT::is_int;
+    constexpr int NT = kG8 * kW8 * 32, NW = kG8 * kW8;
+    constexpr int UNITS = kU8 * 2;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int RS = p.Kc + TT::PAD;             // bytes per staged activation row
+    const int cols = p.T * p.M;                // (term, batch row) columns in use
+    unsigned char *s_ring = smem;                                         // [NW][S][UNITS][32] uint4
+    unsigned char *s_act = s_ring + (size_t)NW * kS8 * UNITS * 512;       // [cols][RS]
+    float *s_red = reinterpret_cast<float *>(s_act + (((size_t)cols * RS + 15) & ~(size_t)15));
+    float *s_out = s_red + kG8 * 2 * kW8 * CG * 128;                      // [G][tiles_per_group][CG*128]
+    float *s_meta = s_out + (size_t)kG8 * p.tiles_per_group * CG * 128;   // [G][tiles_per_group][16][3]
+    float *s_part = s_meta + (size_t)kG8 * p.tiles_per_group * 48;        // [NW][2]
+    float *s_dq = s_part + NW * 2;                                        // [8]
+    float *s_rs = s_dq + 8;                                               // [8]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = warp / kW8, gw = warp % kW8, gtid = tid - group * kW8 * 32;
+    const int g = lane >> 2, c = lane & 3;
+    const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * kG8;
+    const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;
+    const bool has_zero = p.zeros != nullptr;
+    float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
+    float *my_red = s_red + (size_t)group * 2 * kW8 * CG * 128;
+    float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
+    unsigned char *my_ring = s_ring + (size_t)warp * kS8 * UNITS * 512 + lane * 16;
+
+    for (int i = gtid; i < tiles_here * 16; i += kW8 * 32) {
+        const int n = (gg + (i >> 4) * GG) * 16 + (i & 15);
+        const bool in = n < p.N;
+        my_meta[i * 3 + 0] = in ? __ldg(p.scales + n) : 1.0f;
+        my_meta[i * 3 + 1] = (in && has_zero) ? __ldg(p.zeros + n) : 0.0f;
+        my_meta[i * 3 + 2] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
+    }
+    for (int i = tid; i < kG8 * p.tiles_per_group * CG * 128; i += NT) s_out[i] = 0.0f;
+
+    // staged row holding batch column (cg*8 + g), or -1
+    int brow[CG];
+#pragma unroll
+    for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
+
+    // ---- per-row step and sum: max |a| over the whole row first -------------------------------
+    const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
+    for (int m = 0; m < p.M; ++m) {
+        const float *row = p.act + (size_t)m * p.K;
+        float mx = 0.0f, sum = 0.0f;
+        if (vec_ok) {
+            for (int i = tid; i < p.K / 4; i += NT) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(row) + i);
+                mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+        } else {
+            for (int k = tid; k < p.K; k += NT) {
+                const float a = __ldg(row + k);
+                mx = fmaxf(mx, fabsf(a));
+                sum += a;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+        }
+        if (lane == 0) {
+            s_part[warp * 2] = mx;
+            s_part[warp * 2 + 1] = sum;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float bm = 0.0f, bs = 0.0f;
+            for (int w = 0; w < NW; ++w) {
+                bm = fmaxf(bm, s_part[w * 2]);
+                bs += s_part[w * 2 + 1];
+            }
+            const float full = INT ? 16256.0f : 448.0f;
+            s_dq[m] = (bm > 0.0f && isfinite(bm)) ? bm / full : 1.0f;
+            s_rs[m] = bs;
+        }
+        __syncthreads();
+    }
+
+    float accf[CG][4];
+    int acci[CG][4];
+#pragma unroll
+    for (int cg = 0; cg < CG; ++cg)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            accf[cg][r] = 0.0f;
+            acci[cg][r] = 0;
+        }
+    int red_buf = 0;
+
+    const int Kpad = p.KB * KBLK;
+    for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
+        const int kc_len = min(p.Kc, Kpad - k0);
+        const int KBc = kc_len / KBLK;
+        const int kb0 = k0 / KBLK;
+        const int nch = (KBc + kU8 - 1) / kU8;
+        const int cpw = (nch + kW8 - 1) / kW8;
+        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
+        int i_tl = 0, i_j = 0, i_st = 0;
+        auto issue_next = [&]() {
+            const bool valid = i_tl < tiles_here;
+            const int ch = gw + i_j * kW8;
+            const uint4 *tile_src = p.frag + ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
+#pragma unroll
+            for (int u = 0; u < kU8; ++u) {
+                const int kb = ch * kU8 + u;
+                const bool ok = valid && (kb < KBc);
+                const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
+                cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
+                cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
+            }
+            cp_commit();
+            if (++i_j == cpw) {
+                i_j = 0;
+                ++i_tl;
+            }
+            if (++i_st == kS8) i_st = 0;
+        };
+#pragma unroll
+        for (int i = 0; i < kS8 - 1; ++i) issue_next();
+
+        __syncthreads();  // previous pass fully consumed
+        // ---- stage the activation bytes of [k0, k0 + kc_len) --------------------------------
+        for (int m = 0; m < p.M; ++m) {
+            const float *row = p.act + (size_t)m * p.K;
+            const float inv = 1.0f / s_dq[m];
+            auto put = [&](int k, float a) {
+                const float x = a * inv;
+                const int pos = act_pos8<FMT>(k);
+                if (INT) {
+                    int q = __float2int_rn(x);
+                    q = max(-16256, min(16256, q));
+                    const int hi = (q + 64) >> 7;
+                    s_act[(size_t)m * RS + pos] = (unsigned char)(signed char)hi;
+                    s_act[(size_t)(p.M + m) * RS + pos] = (unsigned char)(signed char)(q - hi * 128);
+                } else {
+                    float r = x;
+                    for (int t = 0; t < p.T; ++t) {
+                        const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+                        s_act[(size_t)(t * p.M + m) * RS + pos] = (unsigned char)code;
+                        r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
+                    }
+                }
+            };
+            if (vec_ok) {
+                const int n4 = kc_len / 4;
+                for (int b4 = 0; b4 < n4; b4 += 2 * NT) {
+                    float4 v[2];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int i4 = b4 + q * NT + tid;
+                        v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (i4 < n4 && k0 + i4 * 4 < p.K)
+                            v[q] = __ldg(reinterpret_cast<const float4 *>(row + k0 + i4 * 4));
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int i4 = b4 + q * NT + tid;
+                        if (i4 < n4) {
+                            put(i4 * 4 + 0, v[q].x);
+                            put(i4 * 4 + 1, v[q].y);
+                            put(i4 * 4 + 2, v[q].z);
+                            put(i4 * 4 + 3, v[q].w);
+                        }
+                    }
+                }
+            } else {
+                for (int k = tid; k < kc_len; k += NT) put(k, (k0 + k < p.K) ? __ldg(row + k0 + k) : 0.0f);
+            }
+        }
+        __syncthreads();
+
+        // ---- stream this K range of every tile of the group ----------------------------------
+        int c_st = 0;
+        for (int tl = 0; tl < tiles_here; ++tl)
+        for (int j = 0; j < cpw; ++j) {
+            issue_next();
+            cp_wait<kS8 - 1>();
+            const int ch = gw + j * kW8;
+#pragma unroll
+            for (int u = 0; u < kU8; ++u) {
+                const int slot = c_st * UNITS + u * 2;
+                const uint4 wl = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
+                const uint4 wh = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(slot + 1) * 512);
+                const int kb_s = min(ch * kU8 + u, KBc - 1);
+                // this lane's activation bytes of the k-block: 16 (8-bit codes) or 32 (4-bit)
+                const int boff = kb_s * KBLK + c * (KBLK / 4);
+#pragma unroll
+                for (int v = 0; v < MMAS / 2; ++v) {  // one 16-byte activation vector feeds two MMAs
+                    uint32_t a[2][4];                // [mma][a0 a1 a2 a3]
+                    if (TT::four_bit) {
+                        const uint32_t wl0 = v ? wl.z : wl.x, wl1 = v ? wl.w : wl.y;
+                        const uint32_t wh0 = v ? wh.z : wh.x, wh1 = v ? wh.w : wh.y;
+                        decode4<FMT>(wl0, a[0][0], a[0][2]);
+                        decode4<FMT>(wh0, a[0][1], a[0][3]);
+                        decode4<FMT>(wl1, a[1][0], a[1][2]);
+                        decode4<FMT>(wh1, a[1][1], a[1][3]);
+                    } else {
+                        a[0][0] = wl.x; a[0][2] = wl.y; a[0][1] = wh.x; a[0][3] = wh.y;
+                        a[1][0] = wl.z; a[1][2] = wl.w; a[1][1] = wh.z; a[1][3] = wh.w;
+                    }
+#pragma unroll
+                    for (int cg = 0; cg < CG; ++cg) {
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (brow[cg] >= 0)
+                            b = *reinterpret_cast<const uint4 *>(s_act + (size_t)brow[cg] * RS + boff + v * 16);
+                        if (INT) {
+                            mma_s8(acci[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                            mma_s8(acci[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                        } else {
+                            mma_e4m3(accf[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                            mma_e4m3(accf[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                        }
+                    }
+                }
+            }
+            if (++c_st == kS8) c_st = 0;
+            if (j == cpw - 1) {
+                // last chunk of a tile: fixed-order reduction over the group's warps
+                float *red = my_red + (size_t)red_buf * kW8 * CG * 128;
+#pragma unroll
+                for (int cg = 0; cg < CG; ++cg)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        red[(gw * CG + cg) * 128 + r * 32 + lane] = INT ? (float)acci[cg][r] : accf[cg][r];
+                        acci[cg][r] = 0;
+                        accf[cg][r] = 0.0f;
+                    }
+                group_barrier8(group);
+                for (int e = gtid; e < CG * 128; e += kW8 * 32) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kW8; ++w) s += red[w * CG * 128 + e];
+                    my_out[tl * CG * 128 + e] += s;
+                }
+                red_buf ^= 1;
+            }
+        }
+        cp_wait<0>();
+    }
+    __syncthreads();
+
+    // ---- epilogue ----------------------------------------------------------------------------
+    const int total = tiles_here * 16 * p.M;
+    for (int i = gtid; i < total; i += kW8 * 32) {
+        const int tl = i / (16 * p.M);
+        const int rem = i - tl * 16 * p.M;
+        const int m = rem >> 4, r16 = rem & 15;
+        const int n = (gg + tl * GG) * 16 + r16;
+        if (n >= p.N) continue;
+        auto at = [&](int col) {
+            const int cg = col >> 3, cc = col & 7;
+            return my_out[tl * CG * 128 + cg * 128 + ((r16 >> 3) * 2 + (cc & 1)) * 32 + (r16 & 7) * 4 + (cc >> 1)];
+        };
+        float acc;
+        if (INT) {
+            acc = at(m) * 128.0f + at(p.M + m);
+            if (FMT == FNN_FMT_I4) acc *= 0.0625f;  // operands carried 16*q
+        } else {
+            acc = at(m) + at(p.M + m);
+            if (p.T == 3) acc += at(2 * p.M + m);
+        }
+        const float *meta = my_meta + (tl * 16 + r16) * 3;
+        p.out[(size_t)m * p.N + n] = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f,
+                                                   p.bias != nullptr, meta[2], p.epilogue);
+    }
+}
+
+template <int FMT, int CG>
+int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
+    using TT = T8<FMT>;
+    const fnn_cuda_qweight *w = a.w;
+    P8 p{};
+    p.frag = w->frag;
+    p.scales = w->scales;
+    p.zeros = w->zeros;
+    p.act = a.a;
+    p.out = a.out;
+    p.bias = a.bias;
+    p.M = (int)a.M;
+    p.N = (int)w->N;
+    p.K = (int)w->K;
+    p.KB = (int)div_ceil(w->K, (size_t)TT::KBLK);
+    p.ntiles = (int)div_ceil(w->N, 16);
+    p.T = T;
+    p.epilogue = a.epilogue;
+    const int cols = T * p.M;
+    const int Kpad = p.KB * TT::KBLK;
+    const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * 512;
+    const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * 2 + 16) * 4 + 64;
+    const size_t per_tile = (size_t)kG8 * (CG * 512 + 192);
+    const size_t cap = 226 * 1024;
+    // one block per SM whenever the per-group accumulators of ceil(tiles / groups) tiles fit next to
+    // at least one ring chunk of activations; otherwise more blocks, run in waves
+    const size_t min_act = (size_t)cols * (TT::KBLK * kU8 + TT::PAD) + 16;
+    FNN_REQUIRE(fixed + per_tile + min_act <= cap, FNN_ERR_UNSUPPORTED,
+                "qmatmul: shared memory budget exceeded for M=%d on the 8-bit fragment kernel", p.M);
+    int grid = ctx->sm_count;
+    int tpg = (int)div_ceil((size_t)p.ntiles, (size_t)grid * kG8);
+    const int tpg_max = (int)((cap - fixed - min_act) / per_tile);
+    if (tpg > tpg_max) {
+        tpg = tpg_max;
+        grid = (int)div_ceil((size_t)p.ntiles, (size_t)kG8 * tpg);
+    }
+    if (tpg < 1) tpg = 1;
+    grid = (int)std::min<size_t>((size_t)grid, div_ceil((size_t)p.ntiles, (size_t)kG8));
+    p.tiles_per_group = tpg;
+    const size_t act_budget = cap - fixed - (size_t)tpg * per_tile;
+    int Kc = Kpad;
+    while ((size_t)cols * (Kc + TT::PAD) + 16 > act_budget && Kc > TT::KBLK * kU8)
+        Kc = (Kc / 2 + TT::KBLK - 1) / TT::KBLK * TT::KBLK;
+    p.Kc = Kc;
+    const size_t act_bytes = (((size_t)cols * (Kc + TT::PAD)) + 15) & ~(size_t)15;
+    const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
+    auto kern = qmm_mma8_kernel<FMT, CG>;
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   FNN_ERR_DISPATCH);
+    kern<<<grid, kG8 * kW8 * 32, smem, ctx->stream>>>(p);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    ctx->last_path = "mma";
+    return FNN_OK;
+}
+
+template <int FMT>
+int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    const int M = (int)a.M;
+    // int8 pairs always; e4m3 triples while they fit one 8-column group with the batch, pairs beyond
+    const int T = T8<FMT>::is_int ? 2 : (M <= 2 ? 3 : 2);
+    return (T * M <= 8) ? launch8<FMT, 1>(ctx, a, T) : launch8<FMT, 2>(ctx, a, T);
+}
+
+}  // namespace
+
+bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M) {
+    // Measured on B200: s8 operands beat the fp16 fragment kernel for the integer formats up to
+    // four batch rows; `mma.sync` with e4m3 operands runs at a fraction of the fp16 rate there, so
+    // FP8 / FP4 stay on the fp16 kernel (the e4m3 instantiations remain selectable for comparison).
+    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4) && M >= 1 && M <= 4 && w->N < (1u << 27) &&
+           w->K < (1u << 27);
+}
+
+int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    switch (a.w->fmt) {
+    case FNN_FMT_I8:
+        return launch8_fmt<FNN_FMT_I8>(ctx, a);
+    case FNN_FMT_I4:
+        return launch8_fmt<FNN_FMT_I4>(ctx, a);
+    case FNN_FMT_F8:
+        return launch8_fmt<FNN_FMT_F8>(ctx, a);
+    case FNN_FMT_F4:
+        return launch8_fmt<FNN_FMT_F4>(ctx, a);
+    }
+    return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: the 8-bit fragment kernel does not cover format %d",
+                     a.w->fmt);
+}
+
+}  // namespace fnn

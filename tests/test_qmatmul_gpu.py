@@ -352,8 +352,10 @@ def test_mma_kernel_parity(backend, fmt, kn):
             got = rig.run(x, b, epi, L.PATH_MMA)
             assert backend.last_path() == "mma"
             want = orc.qmatmul(q, x, b, epi)
-            # two-term fp16 activations (M <= 4) keep f32-grade accuracy on exact code formats;
-            # the codebook format rounds centroid*scale to fp16 and larger M uses one fp16 term
+            # up to 8 rows: int8 activation pairs (I8, I4) and e4m3 triples (FP8, FP4 up to 2 rows)
+            # are f32-grade; e4m3 pairs, the fp16 codebook path and M > 8 (one fp16 term) are not
+            # up to 4 rows every exact-code format is f32-grade (int8 pairs for I8 / I4, fp16 hi+lo
+            # for FP8 / FP4); beyond, one fp16 term; the codebook format rounds to fp16 throughout
             tol = TOL_F32 if (m <= 4 and fmt != orc.FMT_I4CB) else TOL_TC
             err = max_err_vs_rms(got, want)
             assert err <= tol, (orc.FMT_NAMES[fmt], kn, m, err)
@@ -375,7 +377,8 @@ def test_mma_kernel_is_deterministic(backend):
 
 
 def test_mma_kernel_flags_activations_outside_fp16_range(backend):
-    q = orc.quantize_kn(orc.FMT_I8, normal(1, (512, 64), 0.02))
+    # FP8 runs on the fp16 fragment kernel (the integer formats use int8 activation pairs there)
+    q = orc.quantize_kn(orc.FMT_F8, normal(1, (512, 64), 0.02))
     rig = Rig(backend, q, 1)
     try:
         x = normal(2, (1, 512), 1.0)
