@@ -15,8 +15,10 @@ whose total size exceeds the 126 MB L2, so every step streams its weights from H
   sweep     the other (format, M) points of the metric, same method (not the headline)
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank holds an 11008-column
-shard of an [4096, 11008*N] layer, activations are replicated and the outputs are
-all-gathered over NCCL: weak scaling, value = bytes all ranks streamed / max-over-ranks time.
+shard of an [4096, 11008*N] layer, activations are replicated and each step is one kernel per
+rank: the shard's GEMV stores its outputs into every rank's gathered buffer over NVLink peer
+memory and waits for the peers' shards.  Weak scaling, value = bytes all ranks streamed /
+max-over-ranks time.
 
 --impl reference times the reference's CPU algorithm (the oracle port) on the host cores.
 """
@@ -362,7 +364,8 @@ def run_ours(args):
                        "l2": f"weights rotate over {layer.replicas} replicas "
                              f"({layer.replicas * K_DIM * N_DIM // 1000000} MB > 126 MB L2)",
                        "parallelism": "single GPU" if world == 1 else
-                                      f"column-sharded x{world}, NCCL all-gather of outputs",
+                                      f"column-sharded x{world}; outputs all-gathered by the GEMV's own "
+                                      "peer stores over NVLink (no collective call)",
                        "algorithmic_bytes_per_step_per_gpu": layer.alg_bytes},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
@@ -405,51 +408,94 @@ NCU_TRAFFIC_BYTES = 45230848
 
 
 def time_sharded(torch, dist, backend, layer, args, world, L):
-    """N > 1: shard GEMV on the compute stream, all-gather of the [M, N/g] outputs on NCCL's
-    stream, overlapped across steps with a two-deep output ring.  Barrier + synchronize on
-    both sides; CUDA events on the compute stream; the caller takes the max over ranks."""
-    m, n = layer.m, layer.n
-    ring = [torch.empty((m, n), dtype=torch.float32, device="cuda") for _ in range(2)]
-    gathered = [torch.empty((world, m, n), dtype=torch.float32, device="cuda") for _ in range(2)]
-    a_dev = torch.empty((m, layer.k), dtype=torch.float32, device="cuda")
-    a_dev.copy_(torch.from_numpy(philox_normal(1, (m, layer.k), 1.0)))
-    comm = torch.cuda.Stream()
-    main = torch.cuda.current_stream()
+    """N > 1: every step is ONE kernel per rank -- the shard's GEMV whose epilogue stores its columns
+    into every rank's gathered buffer over NVLink peer memory and whose last block waits for all
+    peers' shards (fnn_cuda_qmatmul_gather), replayed from a CUDA graph.  Barrier + synchronize on
+    both sides; CUDA events on the launching stream; the caller takes the max over ranks."""
+    import ctypes
+    rank = dist.get_rank()
     lib = backend.lib
-    done = [None, None]
-
-    def step(i):
-        slot = i % 2
-        if done[slot] is not None:
-            main.wait_event(done[slot])          # the gather that read this slot has finished
-        w = layer.weights[i % layer.replicas]
-        rc = lib.fnn_cuda_qmatmul_ptr(backend.ctx, w.handle, a_dev.data_ptr(), ring[slot].data_ptr(),
-                                      None, m, L.EPI_SILU, 0)
-        if rc != 0:
-            raise RuntimeError(L.last_error())
-        ev = torch.cuda.Event()
-        ev.record(main)
-        comm.wait_event(ev)
-        with torch.cuda.stream(comm):
-            dist.all_gather_into_tensor(gathered[slot], ring[slot])
-            d = torch.cuda.Event()
-            d.record(comm)
-        done[slot] = d
-
+    # one shared arena (gather buffers + flags); the layer's weight replicas rotate underneath it
+    fused = FusedGatherLinearReplicas(backend, layer, rank, world, dist)
+    fused.set_activations(philox_normal(1, (layer.m, layer.k), 1.0))
     for i in range(max(args.warmup, 3)):
-        step(i)
-    torch.cuda.synchronize()
+        fused.forward(i)
+    backend.synchronize()
     dist.barrier()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(main)
+    check(lib.fnn_cuda_graph_begin(backend.ctx), layer.fnn)
     for i in range(args.steps):
-        step(i)
-    main.wait_stream(comm)
-    stop.record(main)
-    torch.cuda.synchronize()
+        fused.forward(i)
+    g = ctypes.c_void_p()
+    check(lib.fnn_cuda_graph_end(backend.ctx, ctypes.byref(g)), layer.fnn)
+    check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)   # graph warm-up on every rank
+    backend.synchronize()
     dist.barrier()
-    return float(start.elapsed_time(stop))
+    torch.cuda.synchronize()
+    ms = ctypes.c_float()
+    check(lib.fnn_cuda_timer_start(backend.ctx, 0), layer.fnn)
+    check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)
+    check(lib.fnn_cuda_timer_stop(backend.ctx, 0), layer.fnn)
+    check(lib.fnn_cuda_timer_elapsed_ms(backend.ctx, 0, ctypes.byref(ms)), layer.fnn)
+    backend.synchronize()
+    dist.barrier()
+    t_end = time.time() + 1.5
+    while time.time() < t_end:   # untimed: same load for the clock sampler, in lock step on all ranks
+        check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)
+        backend.synchronize()
+        flag = torch.tensor([1 if time.time() < t_end else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            break
+    lib.fnn_cuda_graph_free(g)
+    fused.close()
+    return float(ms.value)
+
+
+class FusedGatherLinearReplicas:
+    """bench-side driver of fnn_cuda_qmatmul_gather over the Layer's rotating weight replicas."""
+
+    def __init__(self, backend, layer, rank, world, dist):
+        import ctypes
+        self.backend, self.layer, self.rank, self.world = backend, layer, rank, world
+        self.n_stride = -(-layer.n // 4) * 4
+        gather_bytes = 2 * world * layer.m * self.n_stride * 4
+        self.flag_off = -(-gather_bytes // 256) * 256
+        self.a_off = self.flag_off + 256
+        self.arena = backend.allocate_arena(self.a_off + layer.m * layer.k * 4)
+        backend.synchronize()
+        handle = (ctypes.c_uint8 * 64)()
+        check(backend.lib.fnn_cuda_ipc_export(self.arena.handle, handle), layer.fnn)
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle))
+        self.peers = (ctypes.c_void_p * world)()
+        self.opened = []
+        for r in range(world):
+            if r == rank:
+                self.peers[r] = self.arena.device_ptr
+            else:
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r])
+                check(backend.lib.fnn_cuda_ipc_open(backend.ctx, buf, ctypes.byref(p)), layer.fnn)
+                self.peers[r] = p.value
+                self.opened.append(p.value)
+        dist.barrier()
+
+    def set_activations(self, x):
+        self.backend.write_arena(self.arena, self.a_off, np.ascontiguousarray(x, np.float32).tobytes())
+
+    def forward(self, i):
+        from fastnn_b200 import _lib as L
+        layer, b = self.layer, self.backend
+        rc = b.lib.fnn_cuda_qmatmul_gather(
+            b.ctx, layer.weights[i % layer.replicas].handle, self.arena.device_ptr + self.a_off, None,
+            layer.m, L.EPI_SILU, self.rank, self.world, self.peers, 0, self.flag_off, self.n_stride)
+        check(rc, layer.fnn)
+
+    def close(self):
+        self.backend.synchronize()
+        for p in self.opened:
+            self.backend.lib.fnn_cuda_ipc_close(self.backend.ctx, p)
+        self.arena.close()
 
 
 # ------------------------------------------------------------------------------ reference arm

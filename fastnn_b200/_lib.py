@@ -54,6 +54,11 @@ SIGNATURES = {
     "fnn_cuda_qmatmul_ptr": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _int, _int]),
     "fnn_cuda_qmatmul_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _int]),
     "fnn_cuda_last_path": (_c.c_char_p, [_vp]),
+    "fnn_cuda_ipc_export": (_int, [_vp, _vp]),
+    "fnn_cuda_ipc_open": (_int, [_vp, _vp, _c.POINTER(_vp)]),
+    "fnn_cuda_ipc_close": (_int, [_vp, _vp]),
+    "fnn_cuda_qmatmul_gather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
+                                       _sz]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_memcpy": (_int, [_vp, _vp, _sz, _sz, _sz]),
     "fnn_cuda_fill": (_int, [_vp, _vp, _sz, _sz, _f]),

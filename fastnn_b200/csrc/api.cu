@@ -371,6 +371,71 @@ int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_
 
 const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx) { return ctx ? ctx->last_path : ""; }
 
+// ---- column-sharded layers: peer memory and the fused GEMV + all-gather ----------------------
+
+int fnn_cuda_ipc_export(fnn_cuda_arena *arena, void *handle64) {
+    clear_error();
+    FNN_REQUIRE(arena && handle64 && arena->owned, FNN_ERR_MEMORY,
+                "ipc_export: needs an arena allocated by fnn_cuda_arena_alloc");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    FNN_CUDA_CHECK(cudaSetDevice(arena->ctx->device), FNN_ERR_MEMORY);
+    FNN_CUDA_CHECK(cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle64, arena->base), FNN_ERR_MEMORY);
+    return FNN_OK;
+}
+
+int fnn_cuda_ipc_open(fnn_cuda_ctx *ctx, const void *handle64, void **device_ptr) {
+    clear_error();
+    FNN_REQUIRE(ctx && handle64 && device_ptr, FNN_ERR_MEMORY, "ipc_open: null argument");
+    FNN_CUDA_CHECK(cudaSetDevice(ctx->device), FNN_ERR_MEMORY);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    FNN_CUDA_CHECK(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess), FNN_ERR_MEMORY);
+    return FNN_OK;
+}
+
+int fnn_cuda_ipc_close(fnn_cuda_ctx *ctx, void *device_ptr) {
+    if (!ctx || !device_ptr) return FNN_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    FNN_CUDA_CHECK(cudaIpcCloseMemHandle(device_ptr), FNN_ERR_MEMORY);
+    return FNN_OK;
+}
+
+int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
+                            const float *bias_dev, size_t M, int epilogue, int rank, int world,
+                            void *const *peer_bases, size_t gather_offset, size_t flag_offset,
+                            size_t n_stride) {
+    clear_error();
+    FNN_REQUIRE(ctx && w && a_dev && peer_bases, FNN_ERR_DISPATCH, "qmatmul_gather: null argument");
+    FNN_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, FNN_ERR_DISPATCH,
+                "qmatmul_gather: rank %d of %d (at most 8 ranks of one node)", rank, world);
+    FNN_REQUIRE(n_stride >= w->N && (gather_offset & 15u) == 0 && (flag_offset & 15u) == 0,
+                FNN_ERR_DISPATCH, "qmatmul_gather: n_stride %zu < shard width %zu, or misaligned offsets",
+                n_stride, w->N);
+    FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
+                "qmatmul_gather: unknown epilogue %d", epilogue);
+    FNN_REQUIRE(qmm_mma8_supported(w, M) && w->mma_ok, FNN_ERR_UNSUPPORTED,
+                "qmatmul_gather: the fused gather serves I8 / I4 weights with 1..4 batch rows "
+                "(fmt=%d, M=%zu); gather other cases with a collective", w->fmt, M);
+    GatherArgs g{};
+    for (int r = 0; r < world; ++r) {
+        FNN_REQUIRE(peer_bases[r] != nullptr, FNN_ERR_DISPATCH, "qmatmul_gather: peer %d has no buffer", r);
+        g.peer_out[r] = (float *)((uint8_t *)peer_bases[r] + gather_offset);
+        g.peer_flag[r] = (unsigned *)((uint8_t *)peer_bases[r] + flag_offset);
+    }
+    uint8_t *mine = (uint8_t *)peer_bases[rank] + flag_offset;
+    g.step_ctr = (unsigned *)(mine + 8 * sizeof(unsigned));   // flags[8] | step | done
+    g.done_ctr = (int *)(mine + 9 * sizeof(unsigned));
+    g.err_flag = ctx->err_flag;
+    g.rank = rank;
+    g.world = world;
+    g.n_stride = (int)n_stride;
+    int rc = prepare_qmm_mma(ctx, w);
+    if (rc != FNN_OK) return rc;
+    QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, &g};
+    return launch_qmm_mma8(ctx, args);
+}
+
 int fnn_cuda_qweight_prepare(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, int path) {
     clear_error();
     FNN_REQUIRE(ctx && w, FNN_ERR_DISPATCH, "qweight_prepare: null handle");

@@ -170,6 +170,19 @@ __device__ __forceinline__ float finish_output(float dot, float scale, float zer
 }
 
 // ---- launchers implemented in the kernel translation units ---------------------------------
+// Fused all-gather of the outputs over peer memory (column-sharded layers, one rank per GPU).
+// Every rank's shared buffer holds gathered[2 slots][world][M][n_stride] f32 and flags[world] u32;
+// the epilogue stores this rank's columns into every peer's buffer, the last block publishes the
+// step number in every peer's flags[rank] and waits (bounded) for all peers' flags.
+struct GatherArgs {
+    float *peer_out[8];
+    unsigned *peer_flag[8];
+    unsigned *step_ctr;   // local: number of completed steps
+    int *done_ctr;        // local: blocks finished in the current launch
+    int *err_flag;
+    int rank, world, n_stride;
+};
+
 struct QmmArgs {
     const fnn_cuda_qweight *w;
     const float *a;    // [M,K]
@@ -177,6 +190,7 @@ struct QmmArgs {
     const float *bias; // [N] or nullptr
     size_t M;
     int epilogue;
+    const GatherArgs *gather = nullptr;
 };
 
 int launch_qmm_rows(fnn_cuda_ctx *ctx, const QmmArgs &args);

@@ -122,7 +122,18 @@ struct P8 {
     int Kc;      // activations staged per pass (multiple of KBLK)
     int T;       // activation terms (2 for int8; 3 or 2 for e4m3)
     int epilogue;
+    int gather_on;
+    GatherArgs g;
 };
+
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 template <int FMT, int CG>
 __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
@@ -148,6 +159,8 @@ qmm_mma8_kernel(P8 p) {
     const int group = warp / kW8, gw = warp % kW8, gtid = tid - group * kW8 * 32;
     const int g = lane >> 2, c = lane & 3;
     const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * kG8;
+    // fused gather: every block reads the step number before any block can advance it
+    const unsigned step = p.gather_on ? *reinterpret_cast<volatile unsigned *>(p.g.step_ctr) + 1u : 0u;
     const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;
     const bool has_zero = p.zeros != nullptr;
     float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
@@ -394,8 +407,40 @@ qmm_mma8_kernel(P8 p) {
             if (p.T == 3) acc += at(2 * p.M + m);
         }
         const float *meta = my_meta + (tl * 16 + r16) * 3;
-        p.out[(size_t)m * p.N + n] = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f,
-                                                   p.bias != nullptr, meta[2], p.epilogue);
+        const float v = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f,
+                                      p.bias != nullptr, meta[2], p.epilogue);
+        if (!p.gather_on) {
+            p.out[(size_t)m * p.N + n] = v;
+        } else {
+            // this rank's columns go straight into every rank's gathered buffer (plain peer stores)
+            const size_t at_out =
+                (((size_t)(step & 1u) * p.g.world + p.g.rank) * p.M + m) * p.g.n_stride + n;
+            for (int r = 0; r < p.g.world; ++r) p.g.peer_out[r][at_out] = v;
+        }
+    }
+    if (p.gather_on) {
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const int ticket = atomicAdd(p.g.done_ctr, 1);
+            if (ticket == (int)gridDim.x - 1) {
+                // last block of this rank: publish the step, then wait for every peer's shard
+                *p.g.done_ctr = 0;
+                __threadfence_system();
+                for (int r = 0; r < p.g.world; ++r) st_release_sys(p.g.peer_flag[r] + p.g.rank, step);
+                const long long t0 = clock64();
+                for (int r = 0; r < p.g.world; ++r) {
+                    // flags are step counters: a peer that is already one step ahead also satisfies us
+                    while ((int)(ld_acquire_sys(p.g.peer_flag[p.g.rank] + r) - step) < 0) {
+                        if (clock64() - t0 > 2000000000LL) {  // ~1 s: give up, report, return
+                            atomicOr(p.g.err_flag, 0x100);
+                            break;
+                        }
+                    }
+                }
+                *p.g.step_ctr = step;
+            }
+        }
     }
 }
 
@@ -417,6 +462,8 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
     p.ntiles = (int)div_ceil(w->N, 16);
     p.T = T;
     p.epilogue = a.epilogue;
+    p.gather_on = a.gather != nullptr;
+    if (a.gather) p.g = *a.gather;
     const int cols = T * p.M;
     const int Kpad = p.KB * TT::KBLK;
     const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * 512;

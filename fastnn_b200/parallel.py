@@ -100,3 +100,83 @@ class ColumnShardedLinear:
         dist.all_gather_into_tensor(gathered, local, group=self.group)
         cols = [gathered[r, :, : b - a] for r, (a, b) in enumerate(self.bounds)]
         return torch.cat(cols, dim=1)
+
+
+class FusedGatherLinear:
+    """Column shard whose GEMV writes its outputs straight into every rank's gathered buffer over
+    NVLink peer memory (`fnn_cuda_qmatmul_gather`): one kernel per step, no collective call.
+
+    Set-up exchanges CUDA IPC handles of one shared arena per rank through `torch.distributed`
+    (any backend; it is host plumbing).  `forward(a_dev_ptr)` launches the step; afterwards
+    `gathered()` returns this step's full [M, N] rows as a numpy array."""
+
+    FLAG_BYTES = 48  # u32 flags[8] | u32 steps | i32 blocks | pad
+
+    def __init__(self, backend, payload: bytes, meta: QuantizedWeightMeta, rank: int, world: int,
+                 m_max: int = 4, epilogue: int = L.EPI_NONE, group=None):
+        import ctypes
+        import torch.distributed as dist
+        self.ctypes, self.backend, self.rank, self.world = ctypes, backend, rank, world
+        self.epilogue, self.m_max = epilogue, m_max
+        self.bounds = shard_bounds(meta.shape[0], world)
+        sub_payload, sub_meta = shard_rows(payload, meta, rank, world)
+        self.n_local = sub_meta.shape[0]
+        self.n_stride = -(-max(b - a for a, b in self.bounds) // 4) * 4
+        self.weight = backend.upload_qweight(sub_payload, sub_meta)
+        gather_bytes = 2 * world * m_max * self.n_stride * 4
+        self.gather_off, self.flag_off = 0, -(-gather_bytes // 256) * 256
+        self.a_off = self.flag_off + 256
+        self.arena = backend.allocate_arena(self.a_off + m_max * meta.shape[1] * 4)
+        backend.synchronize()
+        handle = (ctypes.c_uint8 * 64)()
+        _check_rc(backend.lib.fnn_cuda_ipc_export(self.arena.handle, handle))
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.peer_ptrs = (ctypes.c_void_p * world)()
+        self._opened = []
+        for r in range(world):
+            if r == rank:
+                self.peer_ptrs[r] = self.arena.device_ptr
+            else:
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r])
+                _check_rc(backend.lib.fnn_cuda_ipc_open(backend.ctx, buf, ctypes.byref(p)))
+                self.peer_ptrs[r] = p.value
+                self._opened.append(p.value)
+        self.calls = 0
+        dist.barrier(group=group)  # every rank has mapped every buffer before the first step
+
+    def set_activations(self, x: np.ndarray) -> None:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        self.m = x.shape[0]
+        self.backend.write_arena(self.arena, self.a_off, x.tobytes())
+
+    def forward(self, m: int = None) -> None:
+        m = self.m if m is None else m
+        rc = self.backend.lib.fnn_cuda_qmatmul_gather(
+            self.backend.ctx, self.weight.handle, self.arena.device_ptr + self.a_off, None, m,
+            self.epilogue, self.rank, self.world, self.peer_ptrs, self.gather_off, self.flag_off,
+            self.n_stride)
+        _check_rc(rc)
+        self.calls += 1
+        self.m = m
+
+    def gathered(self) -> np.ndarray:
+        slot = self.calls & 1
+        per_slot = self.world * self.m * self.n_stride * 4
+        raw = self.backend.read_arena(self.arena, self.gather_off + slot * per_slot, per_slot)
+        full = np.frombuffer(raw, np.float32).reshape(self.world, self.m, self.n_stride)
+        return np.concatenate([full[r, :, : b - a] for r, (a, b) in enumerate(self.bounds)], axis=1)
+
+    def close(self) -> None:
+        self.backend.synchronize()
+        for p in self._opened:
+            self.backend.lib.fnn_cuda_ipc_close(self.backend.ctx, p)
+        self._opened = []
+        self.weight.close()
+        self.arena.close()
+
+
+def _check_rc(rc: int) -> None:
+    if rc != 0:
+        raise BackendError.from_status(rc)

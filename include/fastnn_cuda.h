@@ -178,6 +178,28 @@ int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float
 /* Name of the kernel family the last fnn_cuda_qmatmul on `ctx` launched. */
 const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx);
 
+/* ---- column-sharded layers on the GPUs of one node --------------------------------------------
+ * No counterpart in the reference (it has no collective of any kind).  A layer is sharded by
+ * output columns = contiguous ranges of packed rows, one process per GPU.  Each rank allocates one
+ * shared arena with fnn_cuda_arena_alloc, exports it, and opens its peers':
+ *   [gather_offset] f32 gathered[2 slots][world][M][n_stride]   (n_stride >= widest shard)
+ *   [flag_offset]   u32 flags[8] | u32 steps | i32 blocks       (zero at start, 48 bytes)
+ * fnn_cuda_qmatmul_gather is the GEMV fused with the all-gather: the epilogue stores this rank's
+ * columns into every rank's `gathered[step & 1][rank]` with plain peer stores over NVLink, the last
+ * block publishes the step number in every peer's flags[rank] and waits until all peers have
+ * published theirs, so when the kernel ends the full [M, N] row set of this step is in local memory
+ * (slot = number of calls so far, modulo 2).  The wait is bounded (about one second): if a peer never
+ * arrives the context's error flag is raised and fnn_cuda_sync reports it.  Every rank must make the
+ * same sequence of calls.  Serves I8 / I4 weights with 1..4 batch rows (the HBM-bound case where a
+ * separate collective costs more than the GEMV); gather anything else with a collective. */
+int fnn_cuda_ipc_export(fnn_cuda_arena *arena, void *handle64);
+int fnn_cuda_ipc_open(fnn_cuda_ctx *ctx, const void *handle64, void **device_ptr);
+int fnn_cuda_ipc_close(fnn_cuda_ctx *ctx, void *device_ptr);
+int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
+                            const float *bias_dev, size_t M, int epilogue, int rank, int world,
+                            void *const *peer_bases, size_t gather_offset, size_t flag_offset,
+                            size_t n_stride);
+
 /* ---- remaining plan instructions ---------------------------------------------------
  * Binary ops broadcast by modulo, out[i] = op(a[i % a_len], b[i % b_len])
  * (src/backend/cpu/elementwise.rs:105-130); unary ops ignore b.  Lengths in floats.
