@@ -425,6 +425,7 @@ def time_sharded(torch, dist, backend, layer, args, world, L):
     check(lib.fnn_cuda_graph_begin(backend.ctx), layer.fnn)
     for i in range(args.steps):
         fused.forward(i)
+    fused.wait()   # the timed region ends only when the last step's shards have arrived from every peer
     g = ctypes.c_void_p()
     check(lib.fnn_cuda_graph_end(backend.ctx, ctypes.byref(g)), layer.fnn)
     check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)   # graph warm-up on every rank
@@ -458,9 +459,9 @@ class FusedGatherLinearReplicas:
         import ctypes
         self.backend, self.layer, self.rank, self.world = backend, layer, rank, world
         self.n_stride = -(-layer.n // 4) * 4
-        gather_bytes = 2 * world * layer.m * self.n_stride * 4
-        self.flag_off = -(-gather_bytes // 256) * 256
-        self.a_off = self.flag_off + 256
+        word_bytes = 2 * world * 4 * self.n_stride * 8      # {value, step} words, two slots of 4 rows
+        self.counter_off = -(-word_bytes // 256) * 256
+        self.a_off = self.counter_off + 256
         self.arena = backend.allocate_arena(self.a_off + layer.m * layer.k * 4)
         backend.synchronize()
         handle = (ctypes.c_uint8 * 64)()
@@ -488,8 +489,12 @@ class FusedGatherLinearReplicas:
         layer, b = self.layer, self.backend
         rc = b.lib.fnn_cuda_qmatmul_gather(
             b.ctx, layer.weights[i % layer.replicas].handle, self.arena.device_ptr + self.a_off, None,
-            layer.m, L.EPI_SILU, self.rank, self.world, self.peers, 0, self.flag_off, self.n_stride)
+            layer.m, L.EPI_SILU, self.rank, self.world, self.peers, 0, self.counter_off, self.n_stride)
         check(rc, layer.fnn)
+
+    def wait(self):
+        check(self.backend.lib.fnn_cuda_gather_wait(self.backend.ctx, self.arena.device_ptr, 0, self.counter_off,
+                                                    self.world, self.n_stride, None), self.layer.fnn)
 
     def close(self):
         self.backend.synchronize()

@@ -57,6 +57,7 @@ SIGNATURES = {
     "fnn_cuda_ipc_export": (_int, [_vp, _vp]),
     "fnn_cuda_ipc_open": (_int, [_vp, _vp, _c.POINTER(_vp)]),
     "fnn_cuda_ipc_close": (_int, [_vp, _vp]),
+    "fnn_cuda_gather_wait": (_int, [_vp, _vp, _sz, _sz, _int, _sz, _vp]),
     "fnn_cuda_qmatmul_gather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
                                        _sz]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),

@@ -167,9 +167,9 @@ class CudaBuffer:
         for q in self.qweights.values():
             q.close()
         self.qweights.clear()
-        if self.handle:
+        if self.handle and getattr(self.backend, "ctx", None):  # the context outlives its buffers
             self.backend.lib.fnn_cuda_arena_free(self.handle)
-            self.handle = 0
+        self.handle = 0
 
     def __del__(self):
         try:
@@ -194,9 +194,9 @@ class QWeightHandle:
         return bytes(buf)
 
     def close(self) -> None:
-        if self.handle:
+        if self.handle and getattr(self.backend, "ctx", None):  # never touch a destroyed context
             self.backend.lib.fnn_cuda_qweight_free(self.handle)
-            self.handle = 0
+        self.handle = 0
 
     def __del__(self):
         try:

@@ -403,13 +403,13 @@ int fnn_cuda_ipc_close(fnn_cuda_ctx *ctx, void *device_ptr) {
 
 int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
                             const float *bias_dev, size_t M, int epilogue, int rank, int world,
-                            void *const *peer_bases, size_t gather_offset, size_t flag_offset,
+                            void *const *peer_bases, size_t gather_offset, size_t counter_offset,
                             size_t n_stride) {
     clear_error();
     FNN_REQUIRE(ctx && w && a_dev && peer_bases, FNN_ERR_DISPATCH, "qmatmul_gather: null argument");
     FNN_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, FNN_ERR_DISPATCH,
                 "qmatmul_gather: rank %d of %d (at most 8 ranks of one node)", rank, world);
-    FNN_REQUIRE(n_stride >= w->N && (gather_offset & 15u) == 0 && (flag_offset & 15u) == 0,
+    FNN_REQUIRE(n_stride >= w->N && (gather_offset & 15u) == 0 && (counter_offset & 15u) == 0,
                 FNN_ERR_DISPATCH, "qmatmul_gather: n_stride %zu < shard width %zu, or misaligned offsets",
                 n_stride, w->N);
     FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
@@ -420,12 +420,12 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
     GatherArgs g{};
     for (int r = 0; r < world; ++r) {
         FNN_REQUIRE(peer_bases[r] != nullptr, FNN_ERR_DISPATCH, "qmatmul_gather: peer %d has no buffer", r);
-        g.peer_out[r] = (float *)((uint8_t *)peer_bases[r] + gather_offset);
-        g.peer_flag[r] = (unsigned *)((uint8_t *)peer_bases[r] + flag_offset);
+        g.peer_words[r] = (unsigned long long *)((uint8_t *)peer_bases[r] + gather_offset);
     }
-    uint8_t *mine = (uint8_t *)peer_bases[rank] + flag_offset;
-    g.step_ctr = (unsigned *)(mine + 8 * sizeof(unsigned));   // flags[8] | step | done
-    g.done_ctr = (int *)(mine + 9 * sizeof(unsigned));
+    uint8_t *mine = (uint8_t *)peer_bases[rank] + counter_offset;
+    g.step_ctr = (unsigned *)mine;   // u32 steps | i32 blocks done | i32 rows of the last step
+    g.done_ctr = (int *)(mine + 4);
+    g.last_m = (int *)(mine + 8);
     g.err_flag = ctx->err_flag;
     g.rank = rank;
     g.world = world;
@@ -434,6 +434,18 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
     if (rc != FNN_OK) return rc;
     QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, &g};
     return launch_qmm_mma8(ctx, args);
+}
+
+int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,
+                         int world, size_t n_stride, void *out_dev) {
+    clear_error();
+    FNN_REQUIRE(ctx && my_base && world >= 1 && world <= 8 && n_stride > 0, FNN_ERR_DISPATCH,
+                "gather_wait: bad argument");
+    FNN_REQUIRE(gather_offset % 8 == 0 && counter_offset % 4 == 0, FNN_ERR_DISPATCH,
+                "gather_wait: offsets must be aligned (gather 8, counters 4)");
+    return launch_gather_wait(ctx, (const unsigned long long *)((uint8_t *)my_base + gather_offset),
+                              (const unsigned *)((uint8_t *)my_base + counter_offset), world, (int)n_stride,
+                              (float *)out_dev);
 }
 
 int fnn_cuda_qweight_prepare(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, int path) {

@@ -174,14 +174,18 @@ __device__ __forceinline__ float finish_output(float dot, float scale, float zer
 // Every rank's shared buffer holds gathered[2 slots][world][M][n_stride] f32 and flags[world] u32;
 // the epilogue stores this rank's columns into every peer's buffer, the last block publishes the
 // step number in every peer's flags[rank] and waits (bounded) for all peers' flags.
+// Fused GEMV + all-gather.  Every output travels as one 8-byte word {value bits, step number}: the
+// store is a single access, so a reader that sees the step number of a word also has its value and
+// no fence or flag handshake is needed on either side.
 struct GatherArgs {
-    float *peer_out[8];
-    unsigned *peer_flag[8];
+    unsigned long long *peer_words[8];   // every rank's [2 slots][world][kGatherRows][n_stride] words
     unsigned *step_ctr;   // local: number of completed steps
     int *done_ctr;        // local: blocks finished in the current launch
+    int *last_m;          // local: batch rows of the last completed step
     int *err_flag;
     int rank, world, n_stride;
 };
+constexpr int kGatherRows = 4;   // batch rows a gathered slot holds (the fused path serves M <= 4)
 
 struct QmmArgs {
     const fnn_cuda_qweight *w;
@@ -199,6 +203,8 @@ int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &args);
 int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M);
 int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &args);
+int launch_gather_wait(fnn_cuda_ctx *ctx, const unsigned long long *my_words, const unsigned *counters,
+                       int world, int n_stride, float *out);
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 // shapes automatic dispatch sends to the skinny tensor-core kernel
 static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->mma_ok && w->K >= 512 && w->N >= 64; }

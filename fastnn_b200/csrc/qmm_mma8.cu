@@ -126,13 +126,24 @@ struct P8 {
     GatherArgs g;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// One gathered output: {value bits, step number} in a single 8-byte access at system scope.
+__device__ __forceinline__ void st_word_sys(unsigned long long *p, float v, unsigned step) {
+    const unsigned long long w = ((unsigned long long)step << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+// Polls one word until it carries `step` (or a later one); false after about a second of cycles.
+__device__ __forceinline__ bool wait_word(const unsigned long long *p, unsigned step, unsigned long long &w) {
+    const long long t0 = clock64();
+    for (;;) {
+        w = ld_word_sys(p);
+        if ((int)((unsigned)(w >> 32) - step) >= 0) return true;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
 }
 
 template <int FMT, int CG>
@@ -181,6 +192,24 @@ qmm_mma8_kernel(P8 p) {
     int brow[CG];
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
+
+    // Fused gather: before this step produces anything, the grid checks that every word of the
+    // previous step has arrived in this rank's buffer (one word per thread, bounded polls).  A peer
+    // whose previous step is visible here has finished reading the slot this step overwrites.
+    if (p.gather_on && step > 1u) {
+        const int m_prev = *reinterpret_cast<volatile int *>(p.g.last_m);
+        const unsigned long long *mine =
+            p.g.peer_words[p.g.rank] + (size_t)((step - 1u) & 1u) * p.g.world * kGatherRows * p.g.n_stride;
+        const int per_rank = m_prev * p.g.n_stride;
+        for (int i = blockIdx.x * NT + tid; i < p.g.world * per_rank; i += gridDim.x * NT) {
+            const int r = i / per_rank;
+            unsigned long long w;
+            if (!wait_word(mine + (size_t)r * kGatherRows * p.g.n_stride + (i - r * per_rank), step - 1u, w)) {
+                atomicOr(p.g.err_flag, 0x100);
+                break;
+            }
+        }
+    }
 
     // ---- per-row step and sum: max |a| over the whole row first -------------------------------
     const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
@@ -414,30 +443,28 @@ qmm_mma8_kernel(P8 p) {
         } else {
             // this rank's columns go straight into every rank's gathered buffer (plain peer stores)
             const size_t at_out =
-                (((size_t)(step & 1u) * p.g.world + p.g.rank) * p.M + m) * p.g.n_stride + n;
-            for (int r = 0; r < p.g.world; ++r) p.g.peer_out[r][at_out] = v;
+                (((size_t)(step & 1u) * p.g.world + p.g.rank) * kGatherRows + m) * p.g.n_stride + n;
+            for (int r = 0; r < p.g.world; ++r) st_word_sys(p.g.peer_words[r] + at_out, v, step);
         }
     }
     if (p.gather_on) {
-        __threadfence_system();
+        // columns between the shard's width and the common stride are never computed: block 0 marks
+        // them as arrived so that readers can poll whole rows
+        if (blockIdx.x == 0) {
+            const int pad = p.g.n_stride - p.N;
+            for (int i = tid; i < pad * p.M; i += NT) {
+                const size_t at_out = (((size_t)(step & 1u) * p.g.world + p.g.rank) * kGatherRows + i / pad) *
+                                          p.g.n_stride + p.N + i % pad;
+                for (int r = 0; r < p.g.world; ++r) st_word_sys(p.g.peer_words[r] + at_out, 0.0f, step);
+            }
+        }
         __syncthreads();
         if (tid == 0) {
+            // the last block to finish advances the step counter (every block read it at its start)
             const int ticket = atomicAdd(p.g.done_ctr, 1);
             if (ticket == (int)gridDim.x - 1) {
-                // last block of this rank: publish the step, then wait for every peer's shard
                 *p.g.done_ctr = 0;
-                __threadfence_system();
-                for (int r = 0; r < p.g.world; ++r) st_release_sys(p.g.peer_flag[r] + p.g.rank, step);
-                const long long t0 = clock64();
-                for (int r = 0; r < p.g.world; ++r) {
-                    // flags are step counters: a peer that is already one step ahead also satisfies us
-                    while ((int)(ld_acquire_sys(p.g.peer_flag[p.g.rank] + r) - step) < 0) {
-                        if (clock64() - t0 > 2000000000LL) {  // ~1 s: give up, report, return
-                            atomicOr(p.g.err_flag, 0x100);
-                            break;
-                        }
-                    }
-                }
+                *p.g.last_m = p.M;
                 *p.g.step_ctr = step;
             }
         }
@@ -518,6 +545,36 @@ bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M) {
     // FP8 / FP4 stay on the fp16 kernel (the e4m3 instantiations remain selectable for comparison).
     return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4) && M >= 1 && M <= 4 && w->N < (1u << 27) &&
            w->K < (1u << 27);
+}
+
+// Consumer side of the fused gather: polls (bounded) every word of the last completed step in this
+// rank's buffer and, if `out` is given, writes the values as plain f32 [world][rows][n_stride].
+__global__ void gather_wait_kernel(const unsigned long long *words, const unsigned *counters, int world,
+                                   int n_stride, float *out, int *err_flag) {
+    const unsigned step = counters[0];
+    const int rows = (int)counters[2];
+    if (step == 0u) return;
+    const unsigned long long *slot = words + (size_t)(step & 1u) * world * kGatherRows * n_stride;
+    const int per_rank = rows * n_stride;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * per_rank; i += gridDim.x * blockDim.x) {
+        const int r = i / per_rank;
+        unsigned long long w;
+        if (!wait_word(slot + (size_t)r * kGatherRows * n_stride + (i - r * per_rank), step, w)) {
+            atomicOr(err_flag, 0x100);
+            return;
+        }
+        if (out) out[i] = __uint_as_float((unsigned)w);
+    }
+}
+
+int launch_gather_wait(fnn_cuda_ctx *ctx, const unsigned long long *my_words, const unsigned *counters,
+                       int world, int n_stride, float *out) {
+    const int blocks = (int)div_ceil((size_t)world * kGatherRows * n_stride, 256 * 4);
+    gather_wait_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, ctx->stream>>>(my_words, counters, world, n_stride,
+                                                                        out, ctx->err_flag);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    return FNN_OK;
 }
 
 int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &a) {

@@ -110,7 +110,7 @@ class FusedGatherLinear:
     (any backend; it is host plumbing).  `forward(a_dev_ptr)` launches the step; afterwards
     `gathered()` returns this step's full [M, N] rows as a numpy array."""
 
-    FLAG_BYTES = 48  # u32 flags[8] | u32 steps | i32 blocks | pad
+    ROWS = 4  # batch rows a gathered slot holds
 
     def __init__(self, backend, payload: bytes, meta: QuantizedWeightMeta, rank: int, world: int,
                  m_max: int = 4, epilogue: int = L.EPI_NONE, group=None):
@@ -123,9 +123,12 @@ class FusedGatherLinear:
         self.n_local = sub_meta.shape[0]
         self.n_stride = -(-max(b - a for a, b in self.bounds) // 4) * 4
         self.weight = backend.upload_qweight(sub_payload, sub_meta)
-        gather_bytes = 2 * world * m_max * self.n_stride * 4
-        self.gather_off, self.flag_off = 0, -(-gather_bytes // 256) * 256
-        self.a_off = self.flag_off + 256
+        if not 1 <= m_max <= self.ROWS:
+            raise ValueError(f"the fused gather serves 1..{self.ROWS} batch rows, got m_max={m_max}")
+        word_bytes = 2 * world * self.ROWS * self.n_stride * 8      # {value, step} words, two slots
+        self.gather_off, self.counter_off = 0, -(-word_bytes // 256) * 256
+        self.plain_off = self.counter_off + 256                     # f32 [world][M][n_stride] after wait()
+        self.a_off = self.plain_off + -(-world * self.ROWS * self.n_stride * 4 // 256) * 256
         self.arena = backend.allocate_arena(self.a_off + m_max * meta.shape[1] * 4)
         backend.synchronize()
         handle = (ctypes.c_uint8 * 64)()
@@ -155,16 +158,23 @@ class FusedGatherLinear:
         m = self.m if m is None else m
         rc = self.backend.lib.fnn_cuda_qmatmul_gather(
             self.backend.ctx, self.weight.handle, self.arena.device_ptr + self.a_off, None, m,
-            self.epilogue, self.rank, self.world, self.peer_ptrs, self.gather_off, self.flag_off,
+            self.epilogue, self.rank, self.world, self.peer_ptrs, self.gather_off, self.counter_off,
             self.n_stride)
         _check_rc(rc)
         self.calls += 1
         self.m = m
 
+    def wait(self) -> None:
+        """Enqueue the consumer-side poll for every rank's shard of the last step; it leaves the
+        rows as plain f32 [world][M][n_stride] at `plain_off` of the arena."""
+        _check_rc(self.backend.lib.fnn_cuda_gather_wait(
+            self.backend.ctx, self.arena.device_ptr, self.gather_off, self.counter_off, self.world,
+            self.n_stride, self.arena.device_ptr + self.plain_off))
+
     def gathered(self) -> np.ndarray:
-        slot = self.calls & 1
-        per_slot = self.world * self.m * self.n_stride * 4
-        raw = self.backend.read_arena(self.arena, self.gather_off + slot * per_slot, per_slot)
+        self.wait()
+        nbytes = self.world * self.m * self.n_stride * 4
+        raw = self.backend.read_arena(self.arena, self.plain_off, nbytes)
         full = np.frombuffer(raw, np.float32).reshape(self.world, self.m, self.n_stride)
         return np.concatenate([full[r, :, : b - a] for r, (a, b) in enumerate(self.bounds)], axis=1)
 

@@ -182,23 +182,31 @@ const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx);
  * No counterpart in the reference (it has no collective of any kind).  A layer is sharded by
  * output columns = contiguous ranges of packed rows, one process per GPU.  Each rank allocates one
  * shared arena with fnn_cuda_arena_alloc, exports it, and opens its peers':
- *   [gather_offset] f32 gathered[2 slots][world][M][n_stride]   (n_stride >= widest shard)
- *   [flag_offset]   u32 flags[8] | u32 steps | i32 blocks       (zero at start, 48 bytes)
- * fnn_cuda_qmatmul_gather is the GEMV fused with the all-gather: the epilogue stores this rank's
- * columns into every rank's `gathered[step & 1][rank]` with plain peer stores over NVLink, the last
- * block publishes the step number in every peer's flags[rank] and waits until all peers have
- * published theirs, so when the kernel ends the full [M, N] row set of this step is in local memory
- * (slot = number of calls so far, modulo 2).  The wait is bounded (about one second): if a peer never
- * arrives the context's error flag is raised and fnn_cuda_sync reports it.  Every rank must make the
- * same sequence of calls.  Serves I8 / I4 weights with 1..4 batch rows (the HBM-bound case where a
- * separate collective costs more than the GEMV); gather anything else with a collective. */
+ *   [gather_offset]  u64 words[2 slots][world][4 rows][n_stride]   (n_stride >= widest shard)
+ *   [counter_offset] u32 steps | i32 blocks | i32 rows of the last step   (16 bytes)
+ * both zero at start (fnn_cuda_arena_alloc clears the arena).
+ * fnn_cuda_qmatmul_gather is the GEMV fused with the all-gather.  Every output travels as one 8-byte
+ * word {f32 value, step number} that the epilogue stores into every rank's
+ * words[step & 1][rank][row][column] with one plain peer store over NVLink: a reader that sees the
+ * step number of a word has its value too, so neither side needs a fence or a flag handshake and the
+ * producer never waits.  The consumer polls: the next fnn_cuda_qmatmul_gather on the stream first
+ * checks, one word per thread over its grid, that the previous step has arrived in full (which also
+ * proves that every peer is done reading the slot it is about to overwrite), and
+ * fnn_cuda_gather_wait does the same for the last step and, when out_dev is given, writes the values
+ * there as plain f32 [world][M][n_stride] for any other consumer.  Polls are bounded (about one
+ * second): if a word never arrives the context's error flag is raised and fnn_cuda_sync reports it.
+ * Every rank must make the same sequence of calls.  Serves I8 / I4 weights with 1..4 batch rows (the
+ * HBM-bound case where a separate collective costs more than the GEMV); gather anything else with a
+ * collective. */
 int fnn_cuda_ipc_export(fnn_cuda_arena *arena, void *handle64);
 int fnn_cuda_ipc_open(fnn_cuda_ctx *ctx, const void *handle64, void **device_ptr);
 int fnn_cuda_ipc_close(fnn_cuda_ctx *ctx, void *device_ptr);
 int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
                             const float *bias_dev, size_t M, int epilogue, int rank, int world,
-                            void *const *peer_bases, size_t gather_offset, size_t flag_offset,
+                            void *const *peer_bases, size_t gather_offset, size_t counter_offset,
                             size_t n_stride);
+int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,
+                         int world, size_t n_stride, void *out_dev);
 
 /* ---- remaining plan instructions ---------------------------------------------------
  * Binary ops broadcast by modulo, out[i] = op(a[i % a_len], b[i % b_len])

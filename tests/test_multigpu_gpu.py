@@ -45,6 +45,7 @@ def _rank_main(rank, world, port, ret):
             y = lin.forward(torch.from_numpy(x).cuda())
             torch.cuda.synchronize()
             ok = ok and max_err_vs_rms(y.cpu().numpy(), orc.qmatmul(q, x)) <= 1e-2
+            lin.weight.close()
         backend.close()
     finally:
         ret[rank] = ok
