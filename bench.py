@@ -334,16 +334,16 @@ def run_ours(args):
         ms_total = layer.time_steps(args.steps, args.warmup, L.EPI_SILU, min_seconds=1.5)
         launches = args.steps
     else:
-        ms_total = time_sharded(torch, dist, backend, layer, args, world, L)
-        launches = args.steps
+        ms_total, e2e_n = time_sharded(torch, dist, backend, layer, args, world, L)
+        launches = args.steps + 1 + e2e_n["launches"]
     t_load1 = time.time()
     clocks = sampler.stop(t_load0, t_load1) if rank == 0 else None
     del launches0
 
     if world > 1:
-        t = torch.tensor([ms_total], device="cuda")
+        t = torch.tensor([ms_total, e2e_n["s_per_step"]], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        ms_total, e2e_n["s_per_step"] = float(t[0].item()), float(t[1].item())
     per_step_s = ms_total / args.steps * 1e-3
     total_bytes = layer.alg_bytes * world
     value = total_bytes / per_step_s / 1e9
@@ -391,7 +391,12 @@ def run_ours(args):
             line["sweep"] = run_sweep(fnn, backend, peaks)
     else:
         if rank == 0:
-            line["e2e"] = None
+            line["e2e"] = {"value": round(total_bytes / e2e_n["s_per_step"] / 1e9, 1), "unit": UNIT,
+                           "h2d_bytes_per_step": e2e_n["h2d"] * world, "d2h_bytes_per_step": e2e_n["d2h"] * world,
+                           "us_per_step": round(e2e_n["s_per_step"] * 1e6, 2),
+                           "api": "per rank and step one graph launch: pinned H2D of the activations, "
+                                  "fnn_cuda_qmatmul_gather, fnn_cuda_gather_wait (unpack), pinned D2H of the "
+                                  "gathered rows, synchronize"}
     layer.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -409,9 +414,11 @@ NCU_TRAFFIC_BYTES = 45230848
 
 def time_sharded(torch, dist, backend, layer, args, world, L):
     """N > 1: every step is ONE kernel per rank -- the shard's GEMV whose epilogue stores its columns
-    into every rank's gathered buffer over NVLink peer memory and whose last block waits for all
-    peers' shards (fnn_cuda_qmatmul_gather), replayed from a CUDA graph.  Barrier + synchronize on
-    both sides; CUDA events on the launching stream; the caller takes the max over ranks."""
+    into every rank's gathered buffer over NVLink peer memory as {value, step} words and which first
+    checks that the previous step has arrived from every peer (fnn_cuda_qmatmul_gather), replayed from
+    a CUDA graph that ends with fnn_cuda_gather_wait for the last step.  Barrier + synchronize on both
+    sides; CUDA events on the launching stream; the caller takes the max over ranks.  Returns the
+    device time in ms and the end-to-end (host buffers) measurement."""
     import ctypes
     rank = dist.get_rank()
     lib = backend.lib
@@ -448,8 +455,26 @@ def time_sharded(torch, dist, backend, layer, args, world, L):
         if int(flag.item()) == 0:
             break
     lib.fnn_cuda_graph_free(g)
+    # end to end at N ranks: every step goes host -> device -> all ranks -> host (wall clock, barrier
+    # on both sides, max over ranks by the caller)
+    fused.bind_pinned()
+    xs = [philox_normal(100 + i, (layer.m, layer.k), 1.0) for i in range(8)]
+    e2e_steps = min(args.steps, 2000)
+    for i in range(max(args.warmup, 3)):
+        fused.x_host[...] = xs[i % 8].ravel()
+        fused.step_pinned(i)
+    dist.barrier()
+    t0 = time.perf_counter()
+    acc = 0.0
+    for i in range(e2e_steps):
+        fused.x_host[...] = xs[i % 8].ravel()
+        acc += float(fused.step_pinned(i)[0])
+    dist.barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e = {"s_per_step": e2e_s, "steps": e2e_steps, "h2d": layer.m * layer.k * 4, "d2h": fused.plain_bytes,
+           "launches": 2 * e2e_steps}
     fused.close()
-    return float(ms.value)
+    return float(ms.value), e2e
 
 
 class FusedGatherLinearReplicas:
@@ -461,13 +486,16 @@ class FusedGatherLinearReplicas:
         self.n_stride = -(-layer.n // 4) * 4
         word_bytes = 2 * world * 4 * self.n_stride * 8      # {value, step} words, two slots of 4 rows
         self.counter_off = -(-word_bytes // 256) * 256
-        self.a_off = self.counter_off + 256
+        self.plain_off = self.counter_off + 256           # f32 [world][m][n_stride] written by wait()
+        self.plain_bytes = world * layer.m * self.n_stride * 4
+        self.a_off = self.plain_off + -(-self.plain_bytes // 256) * 256
         self.arena = backend.allocate_arena(self.a_off + layer.m * layer.k * 4)
         backend.synchronize()
         handle = (ctypes.c_uint8 * 64)()
         check(backend.lib.fnn_cuda_ipc_export(self.arena.handle, handle), layer.fnn)
         handles = [None] * world
         dist.all_gather_object(handles, bytes(handle))
+        self.graphs, self.pinned = [], []
         self.peers = (ctypes.c_void_p * world)()
         self.opened = []
         for r in range(world):
@@ -492,12 +520,49 @@ class FusedGatherLinearReplicas:
             layer.m, L.EPI_SILU, self.rank, self.world, self.peers, 0, self.counter_off, self.n_stride)
         check(rc, layer.fnn)
 
-    def wait(self):
+    def wait(self, unpack=False):
+        out = self.arena.device_ptr + self.plain_off if unpack else None
         check(self.backend.lib.fnn_cuda_gather_wait(self.backend.ctx, self.arena.device_ptr, 0, self.counter_off,
-                                                    self.world, self.n_stride, None), self.layer.fnn)
+                                                    self.world, self.n_stride, out), self.layer.fnn)
+
+    def bind_pinned(self):
+        """Host-to-host step per weight replica as one captured graph: pinned H2D of the activations,
+        the fused GEMV + gather, the consumer-side poll that unpacks the gathered rows, pinned D2H."""
+        import ctypes
+        lib, b, layer = self.backend.lib, self.backend, self.layer
+
+        def pinned(nbytes):
+            p = ctypes.c_void_p()
+            check(lib.fnn_cuda_host_alloc(nbytes, ctypes.byref(p)), layer.fnn)
+            self.pinned.append(p.value)
+            return p.value, np.ctypeslib.as_array((ctypes.c_float * (nbytes // 4)).from_address(p.value))
+
+        self.x_ptr, self.x_host = pinned(layer.m * layer.k * 4)
+        self.y_ptr, self.y_host = pinned(self.plain_bytes)
+        for i in range(layer.replicas):
+            check(lib.fnn_cuda_graph_begin(b.ctx), layer.fnn)
+            check(lib.fnn_cuda_arena_write_async(self.arena.handle, self.a_off, self.x_ptr, layer.m * layer.k * 4),
+                  layer.fnn)
+            self.forward(i)
+            self.wait(unpack=True)
+            check(lib.fnn_cuda_arena_read_async(self.arena.handle, self.plain_off, self.y_ptr, self.plain_bytes),
+                  layer.fnn)
+            g = ctypes.c_void_p()
+            check(lib.fnn_cuda_graph_end(b.ctx, ctypes.byref(g)), layer.fnn)
+            self.graphs.append(g)
+
+    def step_pinned(self, i):
+        check(self.backend.lib.fnn_cuda_graph_launch(self.backend.ctx, self.graphs[i % len(self.graphs)]),
+              self.layer.fnn)
+        self.backend.synchronize()
+        return self.y_host
 
     def close(self):
         self.backend.synchronize()
+        for g in self.graphs:
+            self.backend.lib.fnn_cuda_graph_free(g)
+        for ptr in self.pinned:
+            self.backend.lib.fnn_cuda_host_free(ptr)
         for p in self.opened:
             self.backend.lib.fnn_cuda_ipc_close(self.backend.ctx, p)
         self.arena.close()

@@ -187,6 +187,102 @@ struct GatherArgs {
 };
 constexpr int kGatherRows = 4;   // batch rows a gathered slot holds (the fused path serves M <= 4)
 
+#ifdef __CUDACC__
+// One gathered output: {value bits, step number} in a single 8-byte access at system scope.
+__device__ __forceinline__ void st_word_sys(unsigned long long *p, float v, unsigned step) {
+    const unsigned long long w = ((unsigned long long)step << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+// Polls one word until it carries `step` (or a later one); false after about a second of cycles.
+__device__ __forceinline__ bool wait_word(const unsigned long long *p, unsigned step, unsigned long long &w) {
+    const long long t0 = clock64();
+    for (;;) {
+        w = ld_word_sys(p);
+        if ((int)((unsigned)(w >> 32) - step) >= 0) return true;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+
+// Per-thread state of one fused-gather launch.
+struct GatherCursor {
+    unsigned step;                          // the step this launch produces (1, 2, ...)
+    const unsigned long long *prev_words;   // this rank's slot of the previous step
+    int prev_per_rank, prev_total, prev_i;  // words per rank / in all / this thread's first word
+    unsigned long long prev_w0;             // first poll of this thread's first word
+};
+
+// Reads the counters (steps, blocks done, rows of the last step: one 16-byte load; every block does
+// this before any block can advance them) and issues the first poll of the previous step's words.
+__device__ __forceinline__ GatherCursor gather_begin(const GatherArgs &g, int global_tid) {
+    GatherCursor c{};
+    unsigned c0, c1, c2, c3;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3) : "l"(g.step_ctr) : "memory");
+    c.step = c0 + 1u;
+    c.prev_i = global_tid;
+    if (c.step > 1u) {
+        c.prev_words = g.peer_words[g.rank] + (size_t)((c.step - 1u) & 1u) * g.world * kGatherRows * g.n_stride;
+        c.prev_per_rank = (int)c2 * g.n_stride;
+        c.prev_total = g.world * c.prev_per_rank;
+        if (c.prev_i < c.prev_total) {
+            const int r = c.prev_i / c.prev_per_rank;
+            c.prev_w0 = ld_word_sys(c.prev_words + (size_t)r * kGatherRows * g.n_stride +
+                                    (c.prev_i - r * c.prev_per_rank));
+        }
+    }
+    return c;
+}
+
+// The grid checks that every word of the previous step has arrived in this rank's buffer (a few
+// words per thread, bounded polls).  A peer whose previous step is visible here has finished reading
+// the slot this step overwrites.
+__device__ __forceinline__ void gather_check_prev(const GatherArgs &g, const GatherCursor &c, int grid_threads) {
+    bool first = true;
+    for (int i = c.prev_i; i < c.prev_total; i += grid_threads) {
+        const int r = i / c.prev_per_rank;
+        unsigned long long w = c.prev_w0;
+        if (!(first && (int)((unsigned)(w >> 32) - (c.step - 1u)) >= 0) &&
+            !wait_word(c.prev_words + (size_t)r * kGatherRows * g.n_stride + (i - r * c.prev_per_rank),
+                       c.step - 1u, w)) {
+            atomicOr(g.err_flag, 0x100);
+            break;
+        }
+        first = false;
+    }
+}
+
+// This rank's output (m, n) goes straight into every rank's buffer (plain peer stores).
+__device__ __forceinline__ void gather_store(const GatherArgs &g, unsigned step, int m, int n, float v) {
+    const size_t at = (((size_t)(step & 1u) * g.world + g.rank) * kGatherRows + m) * g.n_stride + n;
+    for (int r = 0; r < g.world; ++r) st_word_sys(g.peer_words[r] + at, v, step);
+}
+
+// End of a fused-gather launch (all threads of the block call it).  Columns between the shard's width
+// and the common stride are never computed: block 0 marks them as arrived so that readers can poll
+// whole rows.  The last block to finish advances the step counter.
+__device__ __forceinline__ void gather_finish(const GatherArgs &g, unsigned step, int M, int N) {
+    const int tid = threadIdx.x, NT = blockDim.x;
+    if (blockIdx.x == 0) {
+        const int pad = g.n_stride - N;
+        for (int i = tid; i < pad * M; i += NT) gather_store(g, step, i / pad, N + i % pad, 0.0f);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int ticket = atomicAdd(g.done_ctr, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            *g.done_ctr = 0;
+            *g.last_m = M;
+            *g.step_ctr = step;
+        }
+    }
+}
+#endif
+
 struct QmmArgs {
     const fnn_cuda_qweight *w;
     const float *a;    // [M,K]

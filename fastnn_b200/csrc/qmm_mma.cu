@@ -160,6 +160,8 @@ struct MmaParams {
     int Kc;          // activations staged per pass (multiple of KBLK)
     int split;       // 1: hi/lo activation split (cols m and Mh+m), Mh = 4*CG; 0: Mh = 8*CG
     int epilogue;
+    int gather_on;   // fused all-gather epilogue (one 8-column group only, M <= kGatherRows)
+    GatherArgs g;
 };
 
 // Warp groups per block for a given number of 8-column groups (register budget).
@@ -226,9 +228,56 @@ qmm_mma_kernel(MmaParams p) {
     // group ids interleave across SMs so consecutive tiles land on different SMs
     const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * G;
     const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;  // tiles gg, gg+GG, ...
+    GatherCursor gc{};
+    if (CG == 1 && p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
     const bool has_zero = p.zeros != nullptr;
     float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
     float *my_red = s_red + (size_t)group * 2 * kW * CG * 128;
+
+    unsigned char *my_ring = s_ring + (size_t)warp * S * UNITS * 512 + lane * 16;
+    float *my_ring_bs = s_ring_bs + (size_t)warp * S * UNITS * 32 + lane;
+
+    // ---- pass state and the issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies
+    // go into the ring (an empty group once the warp's items are exhausted).  The first pass's weights
+    // start streaming here, so all of the set-up below runs under the first loads.
+    const int Kpad = p.KB * KBLK;
+    int kc_len = 0, KBc = 0, kb0 = 0, cpw = 0;   // cpw: chunks per warp per tile
+    int i_tl = 0, i_j = 0, i_st = 0;
+    auto issue_next = [&]() {
+        const bool valid = i_tl < tiles_here;
+        const int ch = gw + i_j * kW;
+        const size_t tile_unit = ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int kb = ch * kU + u;
+            const bool ok = valid && (kb < KBc);
+            const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
+                           ok ? 16 : 0);
+                if (FMT == FNN_FMT_I4CB)
+                    cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
+                              ok ? 4 : 0);
+            }
+        }
+        cp_async_commit();
+        if (++i_j == cpw) {
+            i_j = 0;
+            ++i_tl;
+        }
+        if (++i_st == S) i_st = 0;
+    };
+    auto begin_pass = [&](int k0) {
+        kc_len = min(p.Kc, Kpad - k0);
+        KBc = kc_len / KBLK;
+        kb0 = k0 / KBLK;
+        cpw = ((KBc + kU - 1) / kU + kW - 1) / kW;
+        i_tl = 0, i_j = 0, i_st = 0;
+#pragma unroll
+        for (int i = 0; i < S - 1; ++i) issue_next();
+    };
+    begin_pass(0);
 
     // scale / zero / bias of the group's rows: fetched now, used by the epilogue
     float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
@@ -258,8 +307,6 @@ qmm_mma_kernel(MmaParams p) {
         else
             brow[cg] = col < p.M ? col : -1;
     }
-    unsigned char *my_ring = s_ring + (size_t)warp * S * UNITS * 512 + lane * 16;
-    float *my_ring_bs = s_ring_bs + (size_t)warp * S * UNITS * 32 + lane;
 
     float acc[CG][4];
 #pragma unroll
@@ -269,45 +316,11 @@ qmm_mma_kernel(MmaParams p) {
     int red_buf = 0;
     const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
 
-    const int Kpad = p.KB * KBLK;
-    for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
-        const int kc_len = min(p.Kc, Kpad - k0);
-        const int KBc = kc_len / KBLK;
-        const int kb0 = k0 / KBLK;
-        const int nch = (KBc + kU - 1) / kU;
-        const int cpw = (nch + kW - 1) / kW;   // chunks per warp per tile
+    // fused gather: the first poll of the previous step's words was issued at the top
+    if (CG == 1 && p.gather_on && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
 
-        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
-        // (an empty group once the warp's items are exhausted)
-        int i_tl = 0, i_j = 0, i_st = 0;
-        auto issue_next = [&]() {
-            const bool valid = i_tl < tiles_here;
-            const int ch = gw + i_j * kW;
-            const size_t tile_unit = ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
-#pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                const int kb = ch * kU + u;
-                const bool ok = valid && (kb < KBc);
-                const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
-                               ok ? 16 : 0);
-                    if (FMT == FNN_FMT_I4CB)
-                        cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
-                                  ok ? 4 : 0);
-                }
-            }
-            cp_async_commit();
-            if (++i_j == cpw) {
-                i_j = 0;
-                ++i_tl;
-            }
-            if (++i_st == S) i_st = 0;
-        };
-        // the first weights are in flight while the activations are being staged
-#pragma unroll
-        for (int i = 0; i < S - 1; ++i) issue_next();
+    for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
+        if (k0 > 0) begin_pass(k0);   // the first pass was started at the top of the kernel
 
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
         // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------
@@ -487,8 +500,12 @@ qmm_mma_kernel(MmaParams p) {
             r = finish_output(dot, meta[0], meta[1], has_zero ? s_rs[m] : 0.0f, p.bias != nullptr,
                               bias, p.epilogue);
         }
-        p.out[(size_t)m * p.N + n] = r;
+        if (CG == 1 && p.gather_on)
+            gather_store(p.g, gc.step, m, n, r);
+        else
+            p.out[(size_t)m * p.N + n] = r;
     }
+    if (CG == 1 && p.gather_on) gather_finish(p.g, gc.step, p.M, p.N);
 }
 
 // rows layout -> fragment-major layout (zero padded to whole tiles / k-blocks)
@@ -576,6 +593,8 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
     p.ntiles = (int)div_ceil(w->N, 16);
     p.split = split;
     p.epilogue = a.epilogue;
+    p.gather_on = (a.gather != nullptr && CG == 1);
+    if (p.gather_on) p.g = *a.gather;
 
     // One block per SM: weight ring + as much of K as fits beside the reduction buffers.
     const int Kpad = p.KB * T::KBLK;

@@ -126,26 +126,6 @@ struct P8 {
     GatherArgs g;
 };
 
-// One gathered output: {value bits, step number} in a single 8-byte access at system scope.
-__device__ __forceinline__ void st_word_sys(unsigned long long *p, float v, unsigned step) {
-    const unsigned long long w = ((unsigned long long)step << 32) | (unsigned long long)__float_as_uint(v);
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long *p) {
-    unsigned long long w;
-    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-    return w;
-}
-// Polls one word until it carries `step` (or a later one); false after about a second of cycles.
-__device__ __forceinline__ bool wait_word(const unsigned long long *p, unsigned step, unsigned long long &w) {
-    const long long t0 = clock64();
-    for (;;) {
-        w = ld_word_sys(p);
-        if ((int)((unsigned)(w >> 32) - step) >= 0) return true;
-        if (clock64() - t0 > 2000000000LL) return false;
-    }
-}
-
 template <int FMT, int CG>
 __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
 qmm_mma8_kernel(P8 p) {
@@ -170,8 +150,9 @@ qmm_mma8_kernel(P8 p) {
     const int group = warp / kW8, gw = warp % kW8, gtid = tid - group * kW8 * 32;
     const int g = lane >> 2, c = lane & 3;
     const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * kG8;
-    // fused gather: every block reads the step number before any block can advance it
-    const unsigned step = p.gather_on ? *reinterpret_cast<volatile unsigned *>(p.g.step_ctr) + 1u : 0u;
+    GatherCursor gc{};
+    if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
+    const unsigned step = gc.step;
     const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;
     const bool has_zero = p.zeros != nullptr;
     float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
@@ -193,23 +174,41 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
 
-    // Fused gather: before this step produces anything, the grid checks that every word of the
-    // previous step has arrived in this rank's buffer (one word per thread, bounded polls).  A peer
-    // whose previous step is visible here has finished reading the slot this step overwrites.
-    if (p.gather_on && step > 1u) {
-        const int m_prev = *reinterpret_cast<volatile int *>(p.g.last_m);
-        const unsigned long long *mine =
-            p.g.peer_words[p.g.rank] + (size_t)((step - 1u) & 1u) * p.g.world * kGatherRows * p.g.n_stride;
-        const int per_rank = m_prev * p.g.n_stride;
-        for (int i = blockIdx.x * NT + tid; i < p.g.world * per_rank; i += gridDim.x * NT) {
-            const int r = i / per_rank;
-            unsigned long long w;
-            if (!wait_word(mine + (size_t)r * kGatherRows * p.g.n_stride + (i - r * per_rank), step - 1u, w)) {
-                atomicOr(p.g.err_flag, 0x100);
-                break;
-            }
+    // ---- pass state and the issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies
+    // go into the ring.  The first pass's weights start streaming here, before the activations are
+    // even looked at, so the prologue below runs under the first loads.
+    const int Kpad = p.KB * KBLK;
+    int kc_len = 0, KBc = 0, kb0 = 0, cpw = 0;
+    int i_tl = 0, i_j = 0, i_st = 0;
+    auto issue_next = [&]() {
+        const bool valid = i_tl < tiles_here;
+        const int ch = gw + i_j * kW8;
+        const uint4 *tile_src = p.frag + ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
+#pragma unroll
+        for (int u = 0; u < kU8; ++u) {
+            const int kb = ch * kU8 + u;
+            const bool ok = valid && (kb < KBc);
+            const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
+            cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
+            cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
         }
-    }
+        cp_commit();
+        if (++i_j == cpw) {
+            i_j = 0;
+            ++i_tl;
+        }
+        if (++i_st == kS8) i_st = 0;
+    };
+    auto begin_pass = [&](int k0) {
+        kc_len = min(p.Kc, Kpad - k0);
+        KBc = kc_len / KBLK;
+        kb0 = k0 / KBLK;
+        cpw = ((KBc + kU8 - 1) / kU8 + kW8 - 1) / kW8;
+        i_tl = 0, i_j = 0, i_st = 0;
+#pragma unroll
+        for (int i = 0; i < kS8 - 1; ++i) issue_next();
+    };
+    begin_pass(0);
 
     // ---- per-row step and sum: max |a| over the whole row first -------------------------------
     const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
@@ -252,6 +251,9 @@ qmm_mma8_kernel(P8 p) {
         __syncthreads();
     }
 
+    // the first poll of the previous step's words was issued at the top; its latency is hidden by now
+    if (p.gather_on && step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
+
     float accf[CG][4];
     int acci[CG][4];
 #pragma unroll
@@ -263,36 +265,8 @@ qmm_mma8_kernel(P8 p) {
         }
     int red_buf = 0;
 
-    const int Kpad = p.KB * KBLK;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
-        const int kc_len = min(p.Kc, Kpad - k0);
-        const int KBc = kc_len / KBLK;
-        const int kb0 = k0 / KBLK;
-        const int nch = (KBc + kU8 - 1) / kU8;
-        const int cpw = (nch + kW8 - 1) / kW8;
-        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
-        int i_tl = 0, i_j = 0, i_st = 0;
-        auto issue_next = [&]() {
-            const bool valid = i_tl < tiles_here;
-            const int ch = gw + i_j * kW8;
-            const uint4 *tile_src = p.frag + ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
-#pragma unroll
-            for (int u = 0; u < kU8; ++u) {
-                const int kb = ch * kU8 + u;
-                const bool ok = valid && (kb < KBc);
-                const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
-                cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
-                cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
-            }
-            cp_commit();
-            if (++i_j == cpw) {
-                i_j = 0;
-                ++i_tl;
-            }
-            if (++i_st == kS8) i_st = 0;
-        };
-#pragma unroll
-        for (int i = 0; i < kS8 - 1; ++i) issue_next();
+        if (k0 > 0) begin_pass(k0);   // the first pass was started before the activation pass
 
         __syncthreads();  // previous pass fully consumed
         // ---- stage the activation bytes of [k0, k0 + kc_len) --------------------------------
@@ -441,34 +415,10 @@ qmm_mma8_kernel(P8 p) {
         if (!p.gather_on) {
             p.out[(size_t)m * p.N + n] = v;
         } else {
-            // this rank's columns go straight into every rank's gathered buffer (plain peer stores)
-            const size_t at_out =
-                (((size_t)(step & 1u) * p.g.world + p.g.rank) * kGatherRows + m) * p.g.n_stride + n;
-            for (int r = 0; r < p.g.world; ++r) st_word_sys(p.g.peer_words[r] + at_out, v, step);
+            gather_store(p.g, step, m, n, v);
         }
     }
-    if (p.gather_on) {
-        // columns between the shard's width and the common stride are never computed: block 0 marks
-        // them as arrived so that readers can poll whole rows
-        if (blockIdx.x == 0) {
-            const int pad = p.g.n_stride - p.N;
-            for (int i = tid; i < pad * p.M; i += NT) {
-                const size_t at_out = (((size_t)(step & 1u) * p.g.world + p.g.rank) * kGatherRows + i / pad) *
-                                          p.g.n_stride + p.N + i % pad;
-                for (int r = 0; r < p.g.world; ++r) st_word_sys(p.g.peer_words[r] + at_out, 0.0f, step);
-            }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            // the last block to finish advances the step counter (every block read it at its start)
-            const int ticket = atomicAdd(p.g.done_ctr, 1);
-            if (ticket == (int)gridDim.x - 1) {
-                *p.g.done_ctr = 0;
-                *p.g.last_m = p.M;
-                *p.g.step_ctr = step;
-            }
-        }
-    }
+    if (p.gather_on) gather_finish(p.g, step, p.M, p.N);
 }
 
 template <int FMT, int CG>

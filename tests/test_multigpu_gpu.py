@@ -1,6 +1,6 @@
-"""Column-sharded quantized Linear on two GPUs: the fused GEMV + peer-store all-gather kernel and
-the NCCL all-gather wrapper must both reproduce the unsharded oracle result on every rank.
-Needs two CUDA devices (skipped otherwise); one process per GPU."""
+"""Column-sharded quantized Linear on 2 / 4 / 8 GPUs: the fused GEMV + peer-store all-gather kernel
+and the NCCL all-gather wrapper must both reproduce the unsharded oracle result on every rank.
+Needs that many CUDA devices (skipped otherwise); one process per GPU."""
 import os
 
 import numpy as np
@@ -38,6 +38,14 @@ def _rank_main(rank, world, port, ret):
                 got = fused.gathered()
                 want = orc.qmatmul(q, x, None, orc.EPI_SILU)
                 ok = ok and got.shape == want.shape and max_err_vs_rms(got, want) <= 1e-3
+            # several steps in a row with nothing but the kernels' own polls between them
+            x = normal(60, (2, k), 1.0)
+            fused.set_activations(x)
+            for _ in range(7):
+                fused.forward()
+            got = fused.gathered()
+            backend.synchronize()
+            ok = ok and max_err_vs_rms(got, orc.qmatmul(q, x, None, orc.EPI_SILU)) <= 1e-3
             fused.close()
             # NCCL path for what the fused kernel does not serve (here: 16 batch rows)
             lin = ColumnShardedLinear(backend, q.payload, meta, rank, world, epilogue=L.EPI_NONE)
@@ -53,12 +61,12 @@ def _rank_main(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_fused_gather_and_nccl_gather_on_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two CUDA devices")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_gather_and_nccl_gather(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
     import torch.multiprocessing as mp
-    world = 2
-    port = 29600 + (os.getpid() % 500)
+    port = 29600 + (os.getpid() % 500) + world
     ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_rank_main, args=(world, port, ret), nprocs=world, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    assert dict(ret) == {r: True for r in range(world)}
