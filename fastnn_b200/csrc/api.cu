@@ -414,9 +414,9 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
                 n_stride, w->N);
     FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
                 "qmatmul_gather: unknown epilogue %d", epilogue);
-    FNN_REQUIRE(qmm_mma8_supported(w, M) && w->mma_ok, FNN_ERR_UNSUPPORTED,
-                "qmatmul_gather: the fused gather serves I8 / I4 weights with 1..4 batch rows "
-                "(fmt=%d, M=%zu); gather other cases with a collective", w->fmt, M);
+    FNN_REQUIRE(M >= 1 && M <= (size_t)kGatherRows && w->mma_ok && qmm_mma_supported(w, M), FNN_ERR_UNSUPPORTED,
+                "qmatmul_gather: the fused gather serves 1..%d batch rows on the fragment kernels "
+                "(fmt=%d, M=%zu, K=%zu); gather other cases with a collective", kGatherRows, w->fmt, M, w->K);
     GatherArgs g{};
     for (int r = 0; r < world; ++r) {
         FNN_REQUIRE(peer_bases[r] != nullptr, FNN_ERR_DISPATCH, "qmatmul_gather: peer %d has no buffer", r);
@@ -433,7 +433,7 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
     int rc = prepare_qmm_mma(ctx, w);
     if (rc != FNN_OK) return rc;
     QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, &g};
-    return launch_qmm_mma8(ctx, args);
+    return launch_qmm_mma(ctx, args);   // 8-bit operand kernel for I8 / I4, fp16 kernel for the rest
 }
 
 int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,

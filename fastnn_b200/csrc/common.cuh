@@ -160,6 +160,26 @@ __device__ __forceinline__ float apply_act(float x, int epi) {
     }
 }
 
+// The same functions through the hardware exp2 / reciprocal units (relative error of a few 1e-7 on
+// the exponential's result; the reference's own SIMD exp is good to 2e-5,
+// src/backend/cpu/microkernels/activations.rs:336-373).  Used where the epilogue competes with the
+// tensor pipe for issue slots.  tanh(u) = 1 - 2 / (1 + e^(2u)).
+__device__ __forceinline__ float apply_act_fast(float x, int epi) {
+    switch (epi) {
+    case FNN_EPI_RELU:
+        return fmaxf(x, 0.0f);
+    case FNN_EPI_GELU: {
+        const float u = 0.7978846f * (x + 0.044715f * x * x * x);
+        const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+        return 0.5f * x * (1.0f + t);
+    }
+    case FNN_EPI_SILU:
+        return __fdividef(x, 1.0f + __expf(-x));
+    default:
+        return x;
+    }
+}
+
 // dot*scale + zero*sum(a) with the reference's separate roundings
 // (src/backend/cpu/microkernels/mod.rs:293-295), then act(x + bias).
 __device__ __forceinline__ float finish_output(float dot, float scale, float zero, float rowsum,
@@ -168,12 +188,15 @@ __device__ __forceinline__ float finish_output(float dot, float scale, float zer
     if (has_bias) x = __fadd_rn(x, bias);
     return apply_act(x, epi);
 }
+__device__ __forceinline__ float finish_output_fast(float dot, float scale, float zero, float rowsum,
+                                                    bool has_bias, float bias, int epi) {
+    float x = __fadd_rn(__fmul_rn(dot, scale), __fmul_rn(zero, rowsum));
+    if (has_bias) x = __fadd_rn(x, bias);
+    return apply_act_fast(x, epi);
+}
 
 // ---- launchers implemented in the kernel translation units ---------------------------------
 // Fused all-gather of the outputs over peer memory (column-sharded layers, one rank per GPU).
-// Every rank's shared buffer holds gathered[2 slots][world][M][n_stride] f32 and flags[world] u32;
-// the epilogue stores this rank's columns into every peer's buffer, the last block publishes the
-// step number in every peer's flags[rank] and waits (bounded) for all peers' flags.
 // Fused GEMV + all-gather.  Every output travels as one 8-byte word {value bits, step number}: the
 // store is a single access, so a reader that sees the step number of a word also has its value and
 // no fence or flag handshake is needed on either side.

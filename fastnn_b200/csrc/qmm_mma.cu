@@ -237,48 +237,6 @@ qmm_mma_kernel(MmaParams p) {
     unsigned char *my_ring = s_ring + (size_t)warp * S * UNITS * 512 + lane * 16;
     float *my_ring_bs = s_ring_bs + (size_t)warp * S * UNITS * 32 + lane;
 
-    // ---- pass state and the issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies
-    // go into the ring (an empty group once the warp's items are exhausted).  The first pass's weights
-    // start streaming here, so all of the set-up below runs under the first loads.
-    const int Kpad = p.KB * KBLK;
-    int kc_len = 0, KBc = 0, kb0 = 0, cpw = 0;   // cpw: chunks per warp per tile
-    int i_tl = 0, i_j = 0, i_st = 0;
-    auto issue_next = [&]() {
-        const bool valid = i_tl < tiles_here;
-        const int ch = gw + i_j * kW;
-        const size_t tile_unit = ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            const int kb = ch * kU + u;
-            const bool ok = valid && (kb < KBc);
-            const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
-                           ok ? 16 : 0);
-                if (FMT == FNN_FMT_I4CB)
-                    cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
-                              ok ? 4 : 0);
-            }
-        }
-        cp_async_commit();
-        if (++i_j == cpw) {
-            i_j = 0;
-            ++i_tl;
-        }
-        if (++i_st == S) i_st = 0;
-    };
-    auto begin_pass = [&](int k0) {
-        kc_len = min(p.Kc, Kpad - k0);
-        KBc = kc_len / KBLK;
-        kb0 = k0 / KBLK;
-        cpw = ((KBc + kU - 1) / kU + kW - 1) / kW;
-        i_tl = 0, i_j = 0, i_st = 0;
-#pragma unroll
-        for (int i = 0; i < S - 1; ++i) issue_next();
-    };
-    begin_pass(0);
-
     // scale / zero / bias of the group's rows: fetched now, used by the epilogue
     float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
     for (int i = gtid; i < tiles_here * 16; i += kW * 32) {
@@ -319,8 +277,45 @@ qmm_mma_kernel(MmaParams p) {
     // fused gather: the first poll of the previous step's words was issued at the top
     if (CG == 1 && p.gather_on && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
 
+    const int Kpad = p.KB * KBLK;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
-        if (k0 > 0) begin_pass(k0);   // the first pass was started at the top of the kernel
+        const int kc_len = min(p.Kc, Kpad - k0);
+        const int KBc = kc_len / KBLK;
+        const int kb0 = k0 / KBLK;
+        const int nch = (KBc + kU - 1) / kU;
+        const int cpw = (nch + kW - 1) / kW;   // chunks per warp per tile
+
+        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
+        // (an empty group once the warp's items are exhausted)
+        int i_tl = 0, i_j = 0, i_st = 0;
+        auto issue_next = [&]() {
+            const bool valid = i_tl < tiles_here;
+            const int ch = gw + i_j * kW;
+            const size_t tile_unit = ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const int kb = ch * kU + u;
+                const bool ok = valid && (kb < KBc);
+                const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
+                               ok ? 16 : 0);
+                    if (FMT == FNN_FMT_I4CB)
+                        cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
+                                  ok ? 4 : 0);
+                }
+            }
+            cp_async_commit();
+            if (++i_j == cpw) {
+                i_j = 0;
+                ++i_tl;
+            }
+            if (++i_st == S) i_st = 0;
+        };
+        // the first weights are in flight while the activations are being staged
+#pragma unroll
+        for (int i = 0; i < S - 1; ++i) issue_next();
 
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
         // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------

@@ -174,86 +174,6 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
 
-    // ---- pass state and the issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies
-    // go into the ring.  The first pass's weights start streaming here, before the activations are
-    // even looked at, so the prologue below runs under the first loads.
-    const int Kpad = p.KB * KBLK;
-    int kc_len = 0, KBc = 0, kb0 = 0, cpw = 0;
-    int i_tl = 0, i_j = 0, i_st = 0;
-    auto issue_next = [&]() {
-        const bool valid = i_tl < tiles_here;
-        const int ch = gw + i_j * kW8;
-        const uint4 *tile_src = p.frag + ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
-#pragma unroll
-        for (int u = 0; u < kU8; ++u) {
-            const int kb = ch * kU8 + u;
-            const bool ok = valid && (kb < KBc);
-            const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
-            cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
-            cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
-        }
-        cp_commit();
-        if (++i_j == cpw) {
-            i_j = 0;
-            ++i_tl;
-        }
-        if (++i_st == kS8) i_st = 0;
-    };
-    auto begin_pass = [&](int k0) {
-        kc_len = min(p.Kc, Kpad - k0);
-        KBc = kc_len / KBLK;
-        kb0 = k0 / KBLK;
-        cpw = ((KBc + kU8 - 1) / kU8 + kW8 - 1) / kW8;
-        i_tl = 0, i_j = 0, i_st = 0;
-#pragma unroll
-        for (int i = 0; i < kS8 - 1; ++i) issue_next();
-    };
-    begin_pass(0);
-
-    // ---- per-row step and sum: max |a| over the whole row first -------------------------------
-    const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
-    for (int m = 0; m < p.M; ++m) {
-        const float *row = p.act + (size_t)m * p.K;
-        float mx = 0.0f, sum = 0.0f;
-        if (vec_ok) {
-            for (int i = tid; i < p.K / 4; i += NT) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(row) + i);
-                mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-                sum += (v.x + v.y) + (v.z + v.w);
-            }
-        } else {
-            for (int k = tid; k < p.K; k += NT) {
-                const float a = __ldg(row + k);
-                mx = fmaxf(mx, fabsf(a));
-                sum += a;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-        }
-        if (lane == 0) {
-            s_part[warp * 2] = mx;
-            s_part[warp * 2 + 1] = sum;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            float bm = 0.0f, bs = 0.0f;
-            for (int w = 0; w < NW; ++w) {
-                bm = fmaxf(bm, s_part[w * 2]);
-                bs += s_part[w * 2 + 1];
-            }
-            const float full = INT ? 16256.0f : 448.0f;
-            s_dq[m] = (bm > 0.0f && isfinite(bm)) ? bm / full : 1.0f;
-            s_rs[m] = bs;
-        }
-        __syncthreads();
-    }
-
-    // the first poll of the previous step's words was issued at the top; its latency is hidden by now
-    if (p.gather_on && step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
-
     float accf[CG][4];
     int acci[CG][4];
 #pragma unroll
@@ -265,8 +185,82 @@ qmm_mma8_kernel(P8 p) {
         }
     int red_buf = 0;
 
+    const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
+    const int Kpad = p.KB * KBLK;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
-        if (k0 > 0) begin_pass(k0);   // the first pass was started before the activation pass
+        const int kc_len = min(p.Kc, Kpad - k0);
+        const int KBc = kc_len / KBLK;
+        const int kb0 = k0 / KBLK;
+        const int nch = (KBc + kU8 - 1) / kU8;
+        const int cpw = (nch + kW8 - 1) / kW8;
+        // issue-side cursor: the next item (tile, chunk-of-this-warp) whose copies go into the ring
+        int i_tl = 0, i_j = 0, i_st = 0;
+        auto issue_next = [&]() {
+            const bool valid = i_tl < tiles_here;
+            const int ch = gw + i_j * kW8;
+            const uint4 *tile_src = p.frag + ((size_t)(gg + i_tl * GG) * p.KB + kb0) * 64 + lane;
+#pragma unroll
+            for (int u = 0; u < kU8; ++u) {
+                const int kb = ch * kU8 + u;
+                const bool ok = valid && (kb < KBc);
+                const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
+                cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
+                cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
+            }
+            cp_commit();
+            if (++i_j == cpw) {
+                i_j = 0;
+                ++i_tl;
+            }
+            if (++i_st == kS8) i_st = 0;
+        };
+#pragma unroll
+        for (int i = 0; i < kS8 - 1; ++i) issue_next();
+
+        if (k0 == 0) {   // under the first weight loads: the per-row scan of the activations
+            // ---- per-row step and sum: max |a| over the whole row first ---------------------
+            for (int m = 0; m < p.M; ++m) {
+                const float *row = p.act + (size_t)m * p.K;
+                float mx = 0.0f, sum = 0.0f;
+                if (vec_ok) {
+                    for (int i = tid; i < p.K / 4; i += NT) {
+                        const float4 v = __ldg(reinterpret_cast<const float4 *>(row) + i);
+                        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+                        sum += (v.x + v.y) + (v.z + v.w);
+                    }
+                } else {
+                    for (int k = tid; k < p.K; k += NT) {
+                        const float a = __ldg(row + k);
+                        mx = fmaxf(mx, fabsf(a));
+                        sum += a;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+                }
+                if (lane == 0) {
+                    s_part[warp * 2] = mx;
+                    s_part[warp * 2 + 1] = sum;
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    float bm = 0.0f, bs = 0.0f;
+                    for (int w = 0; w < NW; ++w) {
+                        bm = fmaxf(bm, s_part[w * 2]);
+                        bs += s_part[w * 2 + 1];
+                    }
+                    const float full = INT ? 16256.0f : 448.0f;
+                    s_dq[m] = (bm > 0.0f && isfinite(bm)) ? bm / full : 1.0f;
+                    s_rs[m] = bs;
+                }
+                __syncthreads();
+            }
+
+            // the first poll of the previous step's words was issued at the top; its latency is hidden by now
+            if (p.gather_on && step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
+        }
 
         __syncthreads();  // previous pass fully consumed
         // ---- stage the activation bytes of [k0, k0 + kc_len) --------------------------------

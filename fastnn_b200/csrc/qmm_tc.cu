@@ -14,8 +14,8 @@
 //     out[m,n] = act(dq[m]*scale[n]*acc + zero[n]*sum_k a[m,k] + bias[n])
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
 //
-// Warp roles (192 threads): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
-// warps 2-5 = epilogue (one TMEM lane quadrant each).  Every mbarrier wait is bounded: a wait
+// Warp roles (320 threads): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
+// warps 2-9 = epilogue (a TMEM lane quadrant each, two warps per quadrant).  Every mbarrier wait is bounded: a wait
 // that runs out raises the context's error flag, every role leaves its loop, TMEM is freed and
 // the kernel returns.
 #include "common.cuh"
@@ -30,7 +30,8 @@ namespace {
 
 constexpr int kTileN = 128;        // weight rows (output channels) per CTA tile = MMA M
 constexpr int kKBlockBytes = 128;  // bytes of K per pipeline stage = one 128B swizzle row
-constexpr int kThreadsTc = 192;
+constexpr int kEpiWarps = 8;                      // two per TMEM lane quadrant
+constexpr int kThreadsTc = (2 + kEpiWarps) * 32;
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any legitimate wait
 
 enum { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };
@@ -277,7 +278,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
-            mbar_init(&tempty[i], 4);
+            mbar_init(&tempty[i], kEpiWarps);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -363,8 +364,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             }
         }
     } else {
-        // ---------------- epilogue (4 warps, one TMEM lane quadrant each) ----------------
+        // ---------------- epilogue (8 warps: a TMEM lane quadrant each, two warps per quadrant
+        // taking alternate 16-column chunks) ----------------
         const int quad = warp & 3;
+        const int chunk0 = ((warp - 2) >> 2) * 16;
         int as = 0;
         uint32_t aphase = 0;
         const bool has_zero = p.zeros != nullptr;
@@ -378,7 +381,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const float zero = (n_ok && has_zero) ? p.zeros[n] : 0.0f;
             const float bias = (n_ok && p.bias) ? p.bias[n] : 0.0f;
             const uint32_t t_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BNt);
-            for (int c0 = 0; c0 < p.Mb; c0 += 16) {
+            for (int c0 = chunk0; c0 < p.Mb; c0 += 16 * (kEpiWarps / 4)) {
                 uint32_t r[T][16];
 #pragma unroll
                 for (int t = 0; t < T; ++t) tmem_ld16(t_base + (uint32_t)(t * p.Mb + c0), r[t]);
@@ -398,8 +401,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     else
                         acc = __uint_as_float(r[0][j]) + __uint_as_float(r[T > 1 ? 1 : 0][j]);
                     const float dot = acc * p.dq[m];
-                    const float v = finish_output(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
-                                                  p.bias != nullptr, bias, p.epilogue);
+                    const float v = finish_output_fast(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
+                                                       p.bias != nullptr, bias, p.epilogue);
                     if (n_ok) p.out[(size_t)m * p.N + n] = v;  // a warp writes 32 consecutive n
                 }
             }

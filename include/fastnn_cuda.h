@@ -195,8 +195,8 @@ const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx);
  * fnn_cuda_gather_wait does the same for the last step and, when out_dev is given, writes the values
  * there as plain f32 [world][M][n_stride] for any other consumer.  Polls are bounded (about one
  * second): if a word never arrives the context's error flag is raised and fnn_cuda_sync reports it.
- * Every rank must make the same sequence of calls.  Serves I8 / I4 weights with 1..4 batch rows (the
- * HBM-bound case where a separate collective costs more than the GEMV); gather anything else with a
+ * Every rank must make the same sequence of calls.  Serves all five formats with 1..4 batch rows (the
+ * HBM-bound case where a separate collective costs more than the GEMV); gather larger batches with a
  * collective. */
 int fnn_cuda_ipc_export(fnn_cuda_arena *arena, void *handle64);
 int fnn_cuda_ipc_open(fnn_cuda_ctx *ctx, const void *handle64, void **device_ptr);

@@ -25,10 +25,13 @@ def _rank_main(rank, world, port, ret):
     try:
         backend = fnn.CudaBackend(rank, stream=torch.cuda.current_stream().cuda_stream)
         k, n = 1024, 1000   # 1000 columns: shards of 500, not a multiple of the 16-row tile
-        for fmt in (orc.FMT_I8, orc.FMT_I4):
+        for fmt in (orc.FMT_I8, orc.FMT_I4, orc.FMT_F8, orc.FMT_F4, orc.FMT_I4CB):
             q = orc.quantize_kn(fmt, normal(31 + fmt, (k, n), 0.02))
-            meta = fnn.QuantizedWeightMeta(bit_width=q.bit_width, scales=q.scales, zero_points=q.zeros,
-                                           shape=[q.n, q.k], fmt=q.fmt)
+            meta = fnn.QuantizedWeightMeta(
+                bit_width=q.bit_width, scales=q.scales, zero_points=q.zeros, shape=[q.n, q.k], fmt=q.fmt,
+                quant_block_size=32 if fmt == orc.FMT_I4CB else 0,
+                codebooks=[q.codebook] if fmt == orc.FMT_I4CB else [])
+            tol = 1e-2 if fmt == orc.FMT_I4CB else 1e-3
             fused = FusedGatherLinear(backend, q.payload, meta, rank, world, m_max=4, epilogue=L.EPI_SILU)
             for step, m in enumerate((1, 3, 1, 2)):   # slots alternate, M changes between steps
                 x = normal(40 + step, (m, k), 1.0)
@@ -37,7 +40,7 @@ def _rank_main(rank, world, port, ret):
                 backend.synchronize()   # raises if a bounded wait gave up
                 got = fused.gathered()
                 want = orc.qmatmul(q, x, None, orc.EPI_SILU)
-                ok = ok and got.shape == want.shape and max_err_vs_rms(got, want) <= 1e-3
+                ok = ok and got.shape == want.shape and max_err_vs_rms(got, want) <= tol
             # several steps in a row with nothing but the kernels' own polls between them
             x = normal(60, (2, k), 1.0)
             fused.set_activations(x)
@@ -45,7 +48,7 @@ def _rank_main(rank, world, port, ret):
                 fused.forward()
             got = fused.gathered()
             backend.synchronize()
-            ok = ok and max_err_vs_rms(got, orc.qmatmul(q, x, None, orc.EPI_SILU)) <= 1e-3
+            ok = ok and max_err_vs_rms(got, orc.qmatmul(q, x, None, orc.EPI_SILU)) <= tol
             fused.close()
             # NCCL path for what the fused kernel does not serve (here: 16 batch rows)
             lin = ColumnShardedLinear(backend, q.payload, meta, rank, world, epilogue=L.EPI_NONE)
