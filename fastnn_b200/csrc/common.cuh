@@ -195,6 +195,34 @@ __device__ __forceinline__ float finish_output_fast(float dot, float scale, floa
     return apply_act_fast(x, epi);
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched through launch_pdl may start while the kernel before it on the stream is still
+// running: everything that does not depend on that kernel (weight prefetch, scales, shared-memory
+// set-up) runs under its tail, and pdl_wait() blocks until the earlier kernel has completed and its
+// memory is visible.  Every block must reach pdl_wait() before it touches activations, outputs or
+// counters.  Without the launch attribute both instructions do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename P>
+inline cudaError_t launch_pdl(void (*kern)(P), int grid, int block, size_t smem, cudaStream_t stream,
+                              const P &params) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, params);
+}
+#endif
+
 // ---- launchers implemented in the kernel translation units ---------------------------------
 // Fused all-gather of the outputs over peer memory (column-sharded layers, one rank per GPU).
 // Fused GEMV + all-gather.  Every output travels as one 8-byte word {value bits, step number}: the

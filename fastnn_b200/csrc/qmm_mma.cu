@@ -228,8 +228,10 @@ qmm_mma_kernel(MmaParams p) {
     // group ids interleave across SMs so consecutive tiles land on different SMs
     const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * G;
     const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;  // tiles gg, gg+GG, ...
+    // the next kernel on the stream may be set up as soon as an SM has room: its own prologue (scales,
+    // lookup table, first weight copies) then runs under this kernel's tail
+    pdl_launch_dependents();
     GatherCursor gc{};
-    if (CG == 1 && p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
     const bool has_zero = p.zeros != nullptr;
     float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
     float *my_red = s_red + (size_t)group * 2 * kW * CG * 128;
@@ -274,9 +276,6 @@ qmm_mma_kernel(MmaParams p) {
     int red_buf = 0;
     const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
 
-    // fused gather: the first poll of the previous step's words was issued at the top
-    if (CG == 1 && p.gather_on && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
-
     const int Kpad = p.KB * KBLK;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
         const int kc_len = min(p.Kc, Kpad - k0);
@@ -317,6 +316,12 @@ qmm_mma_kernel(MmaParams p) {
 #pragma unroll
         for (int i = 0; i < S - 1; ++i) issue_next();
 
+        if (k0 == 0) {
+            // everything above (scales, lookup table, the first weight copies) is independent of the
+            // kernel before this one on the stream; the activations and the gather counters are not
+            pdl_wait();
+            if (CG == 1 && p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
+        }
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
         // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------
         for (int m0 = 0; m0 < p.M; m0 += 2) {
@@ -378,6 +383,8 @@ qmm_mma_kernel(MmaParams p) {
             }
         }
         __syncthreads();
+        // fused gather: the first poll of the previous step's words was issued before the staging
+        if (CG == 1 && p.gather_on && k0 == 0 && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
         if (has_zero && tid < p.M) {
             float s = s_rs[tid];
             for (int w = 0; w < NW; ++w) s += s_rs_part[w * 64 + tid];
@@ -625,8 +632,7 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
     auto kern = qmm_mma_kernel<FMT, CG>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    kern<<<grid, G * kW * 32, smem, ctx->stream>>>(p);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, G * kW * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     return FNN_OK;
 }

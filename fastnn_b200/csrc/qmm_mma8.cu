@@ -150,9 +150,10 @@ qmm_mma8_kernel(P8 p) {
     const int group = warp / kW8, gw = warp % kW8, gtid = tid - group * kW8 * 32;
     const int g = lane >> 2, c = lane & 3;
     const int gg = group * gridDim.x + blockIdx.x, GG = gridDim.x * kG8;
+    // the next kernel on the stream may be set up as soon as an SM has room: its own prologue (scales,
+    // first weight copies) then runs under this kernel's tail
+    pdl_launch_dependents();
     GatherCursor gc{};
-    if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
-    const unsigned step = gc.step;
     const int tiles_here = gg < p.ntiles ? (p.ntiles - gg + GG - 1) / GG : 0;
     const bool has_zero = p.zeros != nullptr;
     float *my_out = s_out + (size_t)group * p.tiles_per_group * CG * 128;
@@ -218,6 +219,10 @@ qmm_mma8_kernel(P8 p) {
         for (int i = 0; i < kS8 - 1; ++i) issue_next();
 
         if (k0 == 0) {   // under the first weight loads: the per-row scan of the activations
+            // everything above (scales, the first weight copies) is independent of the kernel before
+            // this one on the stream; the activations and the gather counters are not
+            pdl_wait();
+            if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
             // ---- per-row step and sum: max |a| over the whole row first ---------------------
             for (int m = 0; m < p.M; ++m) {
                 const float *row = p.act + (size_t)m * p.K;
@@ -259,7 +264,7 @@ qmm_mma8_kernel(P8 p) {
             }
 
             // the first poll of the previous step's words was issued at the top; its latency is hidden by now
-            if (p.gather_on && step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
+            if (p.gather_on && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
         }
 
         __syncthreads();  // previous pass fully consumed
@@ -382,6 +387,7 @@ qmm_mma8_kernel(P8 p) {
         cp_wait<0>();
     }
     __syncthreads();
+    const unsigned step = gc.step;
 
     // ---- epilogue ----------------------------------------------------------------------------
     const int total = tiles_here * 16 * p.M;
@@ -466,8 +472,7 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
     auto kern = qmm_mma8_kernel<FMT, CG>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    kern<<<grid, kG8 * kW8 * 32, smem, ctx->stream>>>(p);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, kG8 * kW8 * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     ctx->last_path = "mma";
     return FNN_OK;
