@@ -162,6 +162,9 @@ __global__ void __launch_bounds__(256)
 act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
                 float *__restrict__ dq, float *__restrict__ rowsum) {
     __shared__ float s_max[8], s_sum[8];
+    // reads the activations and overwrites planes the previous tensor-core kernel may still read
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x, tid = threadIdx.x;
     const float *row = act + (size_t)m * K;
     float mx = 0.0f, sum = 0.0f;
@@ -267,6 +270,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();   // barrier set-up and the TMEM allocation below run under the previous kernel's tail
     // TMEM columns: two accumulator buffers of BNt columns, power of two >= 32
     uint32_t ncols = 32;
     while ((int)ncols < 2 * BNt) ncols <<= 1;
@@ -293,6 +297,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();   // the activation planes, dq and rowsum come from the kernel before this one
     const uint32_t tmem_base = *s_tmem;
     const int total_tiles = p.n_tiles * p.m_tiles;
 
@@ -484,8 +489,8 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
                                          (size_t)(Mpad - M) * Kp, T, ctx->stream),
                        FNN_ERR_DISPATCH);
-    act_prep_kernel<KIND, T><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
+                   FNN_ERR_DISPATCH);
     ctx->launches++;
 
     CUtensorMap map_w, map_a;
@@ -532,8 +537,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     auto kern = qmm_tc_kernel<KIND, T>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    kern<<<grid, kThreadsTc, smem, ctx->stream>>>(map_w, map_a, p);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, kThreadsTc, smem, ctx->stream, map_w, map_a, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     ctx->last_path = "tc";
     return FNN_OK;
@@ -568,8 +572,8 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
         FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
                                          (size_t)(Mpad - M) * Kp, T, ctx->stream),
                        FNN_ERR_DISPATCH);
-    act_prep_kernel<KIND, T><<<M, 256, 0, ctx->stream>>>(a.a, M, K, Kp, Mpad, bq, dq, rowsum);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
+                   FNN_ERR_DISPATCH);
     ctx->launches++;
 
     CUtensorMap map_w, map_a;
@@ -616,8 +620,7 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
     auto kern = qmm_tc_kernel<KIND, T>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    kern<<<grid, kThreadsTc, smem, ctx->stream>>>(map_w, map_a, p);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, kThreadsTc, smem, ctx->stream, map_w, map_a, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     ctx->last_path = "tc-noalloc";
     return FNN_OK;
