@@ -6,8 +6,9 @@
 // `mma.sync.m16n8k32` as 8-bit operands:
 //   I8   -> s8 operands as stored (no decode at all)
 //   I4   -> s8 operands holding 16*q: two masks per word of eight codes
-//   FP8  -> e4m3 operands as stored
-//   FP4  -> e4m3 codes of the same values through a byte-permute table
+//   FP4  -> s8 operands holding 2*|v| through a byte-permute table, positive and negative codes
+//           in separate operands (two accumulators, subtracted at the end): no sign arithmetic
+//   FP8  -> e4m3 operands as stored (kept for comparison; `mma.sync` on e4m3 is slow on this part)
 // and the f32 activations are rewritten while they are staged, per batch row, as
 //   int8:  a ~= dq * (128*hi + lo)        (15-bit fixed point, exact int32 accumulation)
 //   e4m3:  a ~= dq * (t1 + t2 [+ t3])     (three terms up to 2 batch rows, two beyond)
@@ -31,7 +32,7 @@ constexpr int kG8 = 3;   // groups per block
 template <int FMT>
 struct T8 {
     static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4);
-    static constexpr bool is_int = (FMT == FNN_FMT_I8 || FMT == FNN_FMT_I4);
+    static constexpr bool is_int = (FMT != FNN_FMT_F8);
     static constexpr int KBLK = four_bit ? 128 : 64;       // k per k-block (4 lanes x 16 bytes per row)
     static constexpr int MMAS = four_bit ? 4 : 2;          // m16n8k32 MMAs per k-block
     static constexpr int PAD = four_bit ? 16 : 64;         // activation row padding (bank spread)
@@ -79,25 +80,23 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // Eight 4-bit codes of one word -> the two A registers of one m16n8k32 MMA.
 //   I4: lo = 16*q of codes 0,2,4,6 ; hi = 16*q of codes 1,3,5,7 (the activations are staged in the
 //       matching order 0,2,4,6,1,3,5,7 of each 8-group)
-//   F4: lo = e4m3 codes of elements 0..3, hi = of elements 4..7 (natural order)
-template <int FMT>
-__device__ __forceinline__ void decode4(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    if (FMT == FNN_FMT_I4) {
-        lo = (w << 4) & 0xF0F0F0F0u;
-        hi = w & 0xF0F0F0F0u;
-    } else {
-        // magnitudes 0,.5,1,1.5 | 2,3,4,6 as e4m3; a selector nibble is the 3-bit magnitude code
-        const uint32_t lutA = 0x3C383000u, lutB = 0x4C484440u;
-        const uint32_t mlo = prmt(lutA, lutB, w & 0x7777u);
-        const uint32_t mhi = prmt(lutA, lutB, (w >> 16) & 0x7777u);
-        // sign bytes: the top bit of each byte of (w << 4) / w is the sign of an even / odd code;
-        // selector nibble | 8 replicates that bit across the byte
-        const uint32_t sh = w << 4;
-        const uint32_t slo = prmt(sh, w, 0xD9C8u);  // codes 0,1,2,3 <- sh.b0, w.b0, sh.b1, w.b1
-        const uint32_t shi = prmt(sh, w, 0xFBEAu);  // codes 4,5,6,7 <- sh.b2, w.b2, sh.b3, w.b3
-        lo = mlo | (slo & 0x80808080u);
-        hi = mhi | (shi & 0x80808080u);
-    }
+__device__ __forceinline__ void decode_i4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    lo = (w << 4) & 0xF0F0F0F0u;
+    hi = w & 0xF0F0F0F0u;
+}
+//   F4 (sign | 3-bit magnitude code): the magnitudes 0,.5,1,1.5,2,3,4,6 doubled are the bytes of a
+//   table that prmt indexes with the raw code.  A code with its sign bit set makes prmt return the
+//   replicated top bit of the table byte, i.e. 0 -- so the raw word yields the positive weights
+//   (negative ones as 0) and the word with all sign bits flipped yields the negative weights'
+//   magnitudes: pos/neg operands in natural element order, seven ALU operations per eight weights.
+__device__ __forceinline__ void decode_f4(uint32_t w, uint32_t &plo, uint32_t &phi, uint32_t &nlo,
+                                          uint32_t &nhi) {
+    const uint32_t t0 = 0x03020100u, t1 = 0x0C080604u;
+    const uint32_t f = w ^ 0x88888888u;
+    plo = prmt(t0, t1, w);
+    phi = prmt(t0, t1, w >> 16);
+    nlo = prmt(t0, t1, f);
+    nhi = prmt(t0, t1, f >> 16);
 }
 
 // Staged byte position of activation k inside its row.
@@ -176,13 +175,14 @@ qmm_mma8_kernel(P8 p) {
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
 
     float accf[CG][4];
-    int acci[CG][4];
+    int acci[CG][4], accn[CG][4];   // accn: FP4's negative-weight sums
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             accf[cg][r] = 0.0f;
             acci[cg][r] = 0;
+            accn[cg][r] = 0;
         }
     int red_buf = 0;
 
@@ -336,13 +336,21 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
                 for (int v = 0; v < MMAS / 2; ++v) {  // one 16-byte activation vector feeds two MMAs
                     uint32_t a[2][4];                // [mma][a0 a1 a2 a3]
+                    uint32_t an[2][4];               // FP4 only: magnitudes of the negative weights
                     if (TT::four_bit) {
                         const uint32_t wl0 = v ? wl.z : wl.x, wl1 = v ? wl.w : wl.y;
                         const uint32_t wh0 = v ? wh.z : wh.x, wh1 = v ? wh.w : wh.y;
-                        decode4<FMT>(wl0, a[0][0], a[0][2]);
-                        decode4<FMT>(wh0, a[0][1], a[0][3]);
-                        decode4<FMT>(wl1, a[1][0], a[1][2]);
-                        decode4<FMT>(wh1, a[1][1], a[1][3]);
+                        if (FMT == FNN_FMT_I4) {
+                            decode_i4(wl0, a[0][0], a[0][2]);
+                            decode_i4(wh0, a[0][1], a[0][3]);
+                            decode_i4(wl1, a[1][0], a[1][2]);
+                            decode_i4(wh1, a[1][1], a[1][3]);
+                        } else {
+                            decode_f4(wl0, a[0][0], a[0][2], an[0][0], an[0][2]);
+                            decode_f4(wh0, a[0][1], a[0][3], an[0][1], an[0][3]);
+                            decode_f4(wl1, a[1][0], a[1][2], an[1][0], an[1][2]);
+                            decode_f4(wh1, a[1][1], a[1][3], an[1][1], an[1][3]);
+                        }
                     } else {
                         a[0][0] = wl.x; a[0][2] = wl.y; a[0][1] = wh.x; a[0][3] = wh.y;
                         a[1][0] = wl.z; a[1][2] = wl.w; a[1][1] = wh.z; a[1][3] = wh.w;
@@ -355,6 +363,10 @@ qmm_mma8_kernel(P8 p) {
                         if (INT) {
                             mma_s8(acci[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                             mma_s8(acci[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                            if (FMT == FNN_FMT_F4) {
+                                mma_s8(accn[cg], an[0][0], an[0][1], an[0][2], an[0][3], b.x, b.y);
+                                mma_s8(accn[cg], an[1][0], an[1][1], an[1][2], an[1][3], b.z, b.w);
+                            }
                         } else {
                             mma_e4m3(accf[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                             mma_e4m3(accf[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
@@ -370,8 +382,10 @@ qmm_mma8_kernel(P8 p) {
                 for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        red[(gw * CG + cg) * 128 + r * 32 + lane] = INT ? (float)acci[cg][r] : accf[cg][r];
+                        red[(gw * CG + cg) * 128 + r * 32 + lane] =
+                            INT ? (float)(FMT == FNN_FMT_F4 ? acci[cg][r] - accn[cg][r] : acci[cg][r]) : accf[cg][r];
                         acci[cg][r] = 0;
+                        accn[cg][r] = 0;
                         accf[cg][r] = 0.0f;
                     }
                 group_barrier8(group);
@@ -405,6 +419,7 @@ qmm_mma8_kernel(P8 p) {
         if (INT) {
             acc = at(m) * 128.0f + at(p.M + m);
             if (FMT == FNN_FMT_I4) acc *= 0.0625f;  // operands carried 16*q
+            if (FMT == FNN_FMT_F4) acc *= 0.5f;     // operands carried 2*|v|
         } else {
             acc = at(m) + at(p.M + m);
             if (p.T == 3) acc += at(2 * p.M + m);
@@ -489,10 +504,12 @@ int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 }  // namespace
 
 bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M) {
-    // Measured on B200: s8 operands beat the fp16 fragment kernel for the integer formats up to
-    // four batch rows; `mma.sync` with e4m3 operands runs at a fraction of the fp16 rate there, so
-    // FP8 / FP4 stay on the fp16 kernel (the e4m3 instantiations remain selectable for comparison).
-    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4) && M >= 1 && M <= 4 && w->N < (1u << 27) &&
+    // Measured on B200: s8 operands beat the fp16 fragment kernel up to four batch rows for every
+    // format whose values are small integers (I8, I4, and FP4 doubled); `mma.sync` with e4m3 operands
+    // runs at a fraction of the fp16 rate there, so FP8 stays on the fp16 kernel (the e4m3
+    // instantiation remains selectable for comparison).
+    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4 || w->fmt == FNN_FMT_F4) && M >= 1 && M <= 4 &&
+           w->N < (1u << 27) &&
            w->K < (1u << 27);
 }
 
