@@ -407,9 +407,9 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel
-# (qmm_mma_kernel, I8, K=4096, N=11008, M=1), from the ncu capture summarised in
-# profiles/qmm_mma_i8_m1_config2.md: 45.228 MB read + 2.6 KB written.
-NCU_TRAFFIC_BYTES = 45230848
+# (qmm_mma8_kernel, I8, K=4096, N=11008, M=1), from the ncu capture summarised in
+# profiles/qmm_mma8_i8_m1_config2.md: 45.2326 MB read + 1.3 KB written.
+NCU_TRAFFIC_BYTES = 45233920
 
 
 def time_sharded(torch, dist, backend, layer, args, world, L):
