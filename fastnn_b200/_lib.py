@@ -61,6 +61,8 @@ SIGNATURES = {
     "fnn_cuda_qmatmul_gather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
                                        _sz]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
+    "fnn_cuda_rms_norm": (_int, [_vp, _vp, _sz, _sz, _c.c_longlong, _sz, _sz, _c.c_float, _sz]),
+    "fnn_cuda_softmax": (_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_memcpy": (_int, [_vp, _vp, _sz, _sz, _sz]),
     "fnn_cuda_fill": (_int, [_vp, _vp, _sz, _sz, _f]),
     "fnn_cuda_graph_begin": (_int, [_vp]),

@@ -15,6 +15,7 @@ src/backend/cpu/matmul.rs:177).
 from __future__ import annotations
 
 import ctypes
+import struct
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
@@ -372,6 +373,29 @@ class CudaBackend:
             _check(lib.fnn_cuda_elementwise(self.ctx, _ELEMENTWISE[name], arena.handle, a.offset,
                                             a.size // 4, b.offset, b.size // 4,
                                             instr.output_slice.offset, out_len))
+            return
+        if name == "rms_norm":
+            data, weight = instr.input_slices[0], instr.input_slices[1]
+            n = instr.output_slice.size // 4
+            if instr.param_dims:
+                n = 1
+                for d in instr.param_dims:
+                    n *= env.resolve(d)
+            eps = struct.unpack("<f", struct.pack("<I", instr.params[0] & 0xFFFFFFFF))[0]
+            hidden = instr.params[1] if len(instr.params) > 1 and instr.params[1] > 0 else weight.size // 4
+            _check(lib.fnn_cuda_rms_norm(self.ctx, arena.handle, data.offset, n, weight.offset,
+                                         weight.size // 4, hidden, eps, instr.output_slice.offset))
+            return
+        if name == "softmax":
+            src = instr.input_slices[0]
+            dims = resolve_params(instr.params, instr.param_dims[:2] if instr.param_dims else None, env, 2)
+            n = instr.output_slice.size // 4
+            if instr.param_dims and len(instr.param_dims) > 2:
+                n = 1
+                for d in instr.param_dims[2:]:
+                    n *= env.resolve(d)
+            _check(lib.fnn_cuda_softmax(self.ctx, arena.handle, src.offset, n, max(dims[0], 1),
+                                        max(dims[1], 1), instr.output_slice.offset))
             return
         # no CPU fallback: anything else is not this backend's job
         raise BackendError("UnsupportedOp", f"kernel '{name}' is not implemented by the CUDA backend")

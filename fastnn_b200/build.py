@@ -21,7 +21,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 NVCC = os.environ.get("FNN_NVCC", "/usr/local/cuda/bin/nvcc")
 HOST_CXX = os.environ.get("FNN_HOST_CXX", "/usr/bin/g++")
 
-CUDA_SOURCES = ["api.cu", "repack.cu", "qmm_rows.cu", "qmm_mma.cu", "qmm_mma8.cu", "qmm_tc.cu"]
+CUDA_SOURCES = ["api.cu", "repack.cu", "qmm_rows.cu", "qmm_mma.cu", "qmm_mma8.cu", "qmm_tc.cu", "plan_ops.cu"]
 HOST_SOURCES = ["quantize_host.cpp"]
 
 NVCC_FLAGS = [

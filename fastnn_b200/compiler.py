@@ -7,7 +7,7 @@ It mirrors, by name and behaviour, the reference call stack
 fusion, weight quantization, memory planning, ``backend.compile``) ->
 ``GraphExecutor::execute`` (src/backend/executor.rs:599-858), and the Python entry
 ``AotExecutor`` (src/python/nn.rs:1219-1431).  Only the opcodes on the path exist here:
-Input, Constant, MatMul, Add/Sub/Mul, Relu/Gelu/Silu.
+Input, Constant, MatMul, Add/Sub/Mul, Relu/Gelu/Silu, RMSNorm, Softmax.
 
 The heavy lifting is not here: quantization calls the library's host pass
 (``fnn_quantize_weights``) and every plan instruction runs as a CUDA kernel.
@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes
 import enum
+import struct
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
@@ -38,6 +39,8 @@ class Opcode(enum.Enum):
     Relu = "Relu"
     Gelu = "Gelu"
     Silu = "Silu"
+    RMSNorm = "RMSNorm"
+    Softmax = "Softmax"
 
 
 @dataclass
@@ -254,6 +257,18 @@ class GraphBuilder:
     def silu(self, x):
         return self._unary(Opcode.Silu, x)
 
+    def rms_norm(self, x: GraphTensor, weight: GraphTensor, eps: float = 1e-5) -> GraphTensor:
+        """src/ir/builder.rs:1624: RMSNorm(input, weight) with attribute `eps`."""
+        node = self.graph.add(Opcode.RMSNorm, [x.node_id(), weight.node_id()], TensorType.new(x.shape()))
+        node.attrs["eps"] = repr(float(eps))
+        return GraphTensor(self, node.id)
+
+    def softmax(self, x: GraphTensor, dim: int = -1) -> GraphTensor:
+        """src/ir/builder.rs:816-828: Softmax with attribute `axis`."""
+        node = self.graph.add(Opcode.Softmax, [x.node_id()], TensorType.new(x.shape()))
+        node.attrs["axis"] = str(int(dim))
+        return GraphTensor(self, node.id)
+
     def recorded_input_ids(self) -> List[int]:
         return list(self._inputs)
 
@@ -443,7 +458,8 @@ def plan_memory(graph: ComputeGraph) -> MemoryPlan:
     slots: Dict[int, Slot] = {}
     free: List[Slot] = []
     top = 0
-    elementwise = (Opcode.Add, Opcode.Sub, Opcode.Mul, Opcode.Relu, Opcode.Gelu, Opcode.Silu)
+    elementwise = (Opcode.Add, Opcode.Sub, Opcode.Mul, Opcode.Relu, Opcode.Gelu, Opcode.Silu,
+                   Opcode.RMSNorm, Opcode.Softmax)   # both row kernels work in place
     for step, n in enumerate(order):
         size = max(n.output_type.byte_size(), 4)
         padded = -(-size // _ALIGN) * _ALIGN
@@ -582,6 +598,35 @@ def lower_to_plan(graph: ComputeGraph, memory_plan: MemoryPlan) -> ExecutablePla
             instructions.append(CallKernel(_UNARY[n.opcode],
                                            [_slice(memory_plan, i) for i in n.inputs], out, [],
                                            node_id=n.id, param_dims=list(n.output_type.shape)))
+            continue
+        if n.opcode == Opcode.RMSNorm:
+            # kernel "rms_norm", params [eps bits] (src/backend/cpu/mod.rs:1526-1545); params[1] carries
+            # the hidden size so that batched inputs normalise rows of weight-length
+            eps = float(n.attrs.get("eps", "1e-5"))
+            hidden = graph.get_node(n.inputs[1]).output_type.numel_max()
+            bits = struct.unpack("<I", struct.pack("<f", eps))[0]
+            instructions.append(CallKernel("rms_norm", [_slice(memory_plan, i) for i in n.inputs], out,
+                                           [bits, int(hidden)], node_id=n.id,
+                                           param_dims=list(n.output_type.shape)))
+            continue
+        if n.opcode == Opcode.Softmax:
+            # kernel "softmax", params [axis_dim, stride] (src/backend/cpu/mod.rs:1002-1050)
+            shape = list(n.output_type.shape)
+            axis = int(n.attrs.get("axis", "0"))
+            axis = axis + len(shape) if axis < 0 else axis
+            if not 0 <= axis < len(shape):
+                raise BackendError("Compilation", f"softmax axis {axis} outside rank {len(shape)}")
+            stride = 1
+            for d in shape[axis + 1:]:
+                if isinstance(d, str):
+                    raise BackendError("UnsupportedOp", "softmax over a non-innermost axis needs static "
+                                                        "trailing dimensions")
+                stride *= int(d)
+            axis_dim = shape[axis]
+            instructions.append(CallKernel(
+                "softmax", [_slice(memory_plan, n.inputs[0])], out,
+                [SYMBOL_DIM_MAX if isinstance(axis_dim, str) else int(axis_dim), stride], node_id=n.id,
+                param_dims=[axis_dim, stride] + shape))
             continue
         raise BackendError("UnsupportedOp", f"opcode {n.opcode} is not on the CUDA backend's path")
     return ExecutablePlan(instructions, memory_plan.total_size, list(range(len(instructions))))
@@ -746,7 +791,7 @@ class AotExecutor:
     """Python-facing executor with the constructor of fastnn's `AotExecutor`
     (src/python/nn.rs:1221-1364): ONNX-style node dicts + a parameter dict.  `params` become
     `Constant` nodes (src/onnx/converter.rs:114-133), `Gemm` lowers to matmul (+ add)
-    (:290-318).  Supported op_types: MatMul, Gemm (transB = 0), Add, Relu, Gelu, Silu."""
+    (:290-318).  Supported op_types: MatMul, Gemm (transB = 0), Add, Relu, Gelu, Silu, RMSNorm, Softmax."""
 
     def __init__(self, nodes: Sequence[Dict[str, object]], params: Dict[str, np.ndarray],
                  input_names: Sequence[str], output_names: Sequence[str],
@@ -791,6 +836,10 @@ class AotExecutor:
                 r = gb.gelu(t[0])
             elif op in ("Silu", "Swish"):
                 r = gb.silu(t[0])
+            elif op in ("RMSNorm", "RmsNorm", "SimplifiedLayerNormalization"):
+                r = gb.rms_norm(t[0], t[1], float(nd.get("eps", nd.get("epsilon", 1e-5))))
+            elif op == "Softmax":
+                r = gb.softmax(t[0], int(nd.get("axis", -1)))
             else:
                 raise BackendError("UnsupportedOp", f"op_type '{op}' is not on the CUDA path")
             env[outs[0]] = r

@@ -217,6 +217,18 @@ int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_
                          size_t a_len, size_t b_offset, size_t b_len, size_t out_offset,
                          size_t out_len);
 /* Instruction::MemCopy and Instruction::Fill (src/backend/mod.rs:82-89). */
+/* rms_norm over rows of row_size floats: out = in / sqrt(mean(in^2) + eps) * w[i]
+ * (src/backend/cpu/microkernels/ops.rs:979-1008).  w_offset < 0: no weight.  The caller passes the
+ * row size: the hidden size (= weight length), as the reference's fused residual variant does
+ * (tests/residual_add_norm.rs:327-355); its unfused dispatch arm derives len / w_len instead
+ * (src/backend/cpu/mod.rs:5053-5075).  out may be in. */
+int fnn_cuda_rms_norm(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t in_offset, size_t len,
+                      long long w_offset, size_t w_len, size_t row_size, float eps, size_t out_offset);
+/* softmax along an axis of axis_dim elements that are `stride` floats apart; len / axis_dim rows
+ * (kernel "softmax", params [axis_dim, stride]: src/backend/cpu/mod.rs:1002-1050, 3488-3514;
+ * src/backend/cpu/microkernels/ops.rs:1363-1397).  out may be in. */
+int fnn_cuda_softmax(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t in_offset, size_t len,
+                     size_t axis_dim, size_t stride, size_t out_offset);
 int fnn_cuda_memcpy(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset,
                     size_t src_offset, size_t bytes);
 int fnn_cuda_fill(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t offset, size_t bytes,

@@ -83,6 +83,10 @@ def lib() -> ctypes.CDLL:
     L.orc_epilogue.restype = None
     L.orc_add_broadcast.argtypes = [c_vp, c_sz, c_vp, c_sz, c_vp, c_sz]
     L.orc_add_broadcast.restype = None
+    L.orc_rms_norm.argtypes = [c_vp, c_sz, c_vp, c_sz, c_sz, ctypes.c_float, c_vp]
+    L.orc_rms_norm.restype = None
+    L.orc_softmax.argtypes = [c_vp, c_sz, c_sz, c_sz, c_vp]
+    L.orc_softmax.restype = None
     L.orc_simd_level.restype = c_int
     L.orc_physical_cores.restype = c_int
     L.orc_k_block_size.restype = c_sz
@@ -268,6 +272,27 @@ def add_broadcast(a: np.ndarray, b: np.ndarray, out_len: int) -> np.ndarray:
     out = np.empty(out_len, dtype=np.float32)
     lib().orc_add_broadcast(_p(a), a.size, _p(b), b.size, _p(out), out_len)
     return out
+
+
+def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float, mode: int = MODE_INTENDED) -> np.ndarray:
+    """Rows of weight.size elements (the hidden size; one row when weight is empty).  MODE_AS_WRITTEN
+    reproduces the unfused dispatch arm's row size x.size // weight.size
+    (src/backend/cpu/mod.rs:5053-5075)."""
+    x, weight = _f32(x), _f32(weight).reshape(-1)
+    row = x.size if weight.size == 0 else (weight.size if mode == MODE_INTENDED else x.size // weight.size)
+    out = np.empty(x.size, dtype=np.float32)
+    lib().orc_rms_norm(_p(x.reshape(-1)), x.size, _p(weight) if weight.size else None, weight.size,
+                       row, ctypes.c_float(eps), _p(out))
+    return out.reshape(x.shape)
+
+
+def softmax(x: np.ndarray, axis: int = -1) -> np.ndarray:
+    x = _f32(x)
+    axis = axis % x.ndim
+    stride = int(np.prod(x.shape[axis + 1:], dtype=np.int64)) if axis + 1 < x.ndim else 1
+    out = np.empty(x.size, dtype=np.float32)
+    lib().orc_softmax(_p(x.reshape(-1)), x.size, x.shape[axis], stride, _p(out))
+    return out.reshape(x.shape)
 
 
 def host_info() -> dict:

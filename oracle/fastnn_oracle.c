@@ -627,6 +627,44 @@ void orc_add_broadcast(const float *a, size_t a_len, const float *b, size_t b_le
     for (size_t i = 0; i < out_len; ++i) out[i] = a[i % a_len] + b[i % b_len];
 }
 
+/* src/backend/cpu/microkernels/ops.rs:979-1008 (rms_norm_f32_scalar). */
+void orc_rms_norm(const float *in, size_t n, const float *w, size_t w_len, size_t row_size, float eps,
+                  float *out) {
+    if (row_size == 0) return;
+    size_t rows = n / row_size;
+    for (size_t r = 0; r < rows; ++r) {
+        const float *x = in + r * row_size;
+        float sq = 0.0f;
+        for (size_t i = 0; i < row_size; ++i) sq += x[i] * x[i];
+        float rms = sqrtf(sq / (float)row_size + eps);
+        for (size_t i = 0; i < row_size; ++i) {
+            float wi = i < w_len ? w[i] : 1.0f;
+            out[r * row_size + i] = x[i] / rms * wi;
+        }
+    }
+}
+
+/* src/backend/cpu/microkernels/ops.rs:1363-1397 (softmax_f32_scalar_strided). */
+void orc_softmax(const float *in, size_t n, size_t axis_dim, size_t stride, float *out) {
+    if (axis_dim == 0) axis_dim = 1;
+    if (stride == 0) stride = 1;
+    size_t rows = n / axis_dim;
+    for (size_t r = 0; r < rows; ++r) {
+        size_t base = (r / stride) * axis_dim * stride + (r % stride);
+        float mx = -INFINITY;
+        for (size_t i = 0; i < axis_dim; ++i)
+            if (in[base + i * stride] > mx) mx = in[base + i * stride];
+        float sum = 0.0f;
+        for (size_t i = 0; i < axis_dim; ++i) {
+            float e = expf(in[base + i * stride] - mx);
+            out[base + i * stride] = e;
+            sum += e;
+        }
+        if (sum > 0.0f)
+            for (size_t i = 0; i < axis_dim; ++i) out[base + i * stride] /= sum;
+    }
+}
+
 /* src/backend/cpu/microkernels/gemm.rs:1982-2088 (gemm_batch_packed_simd), reached via
  * gemm_cpu_flat (:1610-1619) from quantized_matmul_dispatch (src/backend/cpu/matmul.rs:214-221).
  * Threads over batch rows only when M >= physical cores (:2019-2035). */

@@ -91,6 +91,18 @@ void orc_epilogue(float *out, size_t len, size_t n, const float *bias, int epilo
 void orc_add_broadcast(const float *a, size_t a_len, const float *b, size_t b_len,
                        float *out, size_t out_len);
 
+/* rms_norm over rows of row_size elements: out = in / sqrt(mean(in^2) + eps) * w[i] (w = 1 beyond
+ * w_len).  src/backend/cpu/microkernels/ops.rs:979-1008.  The fused residual variant takes the
+ * hidden size (= weight length) as row size (tests/residual_add_norm.rs:327-355); the unfused
+ * dispatch arm derives input_len / weight_len instead (src/backend/cpu/mod.rs:5053-5075), which
+ * equals the hidden size only for square inputs -- callers choose by passing row_size. */
+void orc_rms_norm(const float *in, size_t n, const float *w, size_t w_len, size_t row_size, float eps,
+                  float *out);
+
+/* softmax plan instruction over the axis of size axis_dim whose elements are `stride` apart;
+ * n / axis_dim rows.  src/backend/cpu/microkernels/ops.rs:1363-1397. */
+void orc_softmax(const float *in, size_t n, size_t axis_dim, size_t stride, float *out);
+
 /* Introspection used by the CPU-baseline report. */
 int orc_simd_level(void);      /* 0 scalar, 2 avx2+fma, 5 avx512f */
 int orc_physical_cores(void);

@@ -10,6 +10,7 @@ from fastnn_b200 import _lib as L
 from fastnn_b200.compiler import (GraphBuilder, GraphExecutor, TensorType, WeightDtype,
                                   eliminate_dead_code, fuse_operators, lower_to_plan, plan_memory,
                                   quantize_weights)
+from fastnn_b200.backend import CallKernel
 from helpers import normal
 
 
@@ -186,3 +187,59 @@ def test_quantize_argument_validation():
     gb = GraphBuilder()
     with pytest.raises(fnn.BackendError):
         gb.compile_and_execute_with_quantize([], RecordingBackend(), [], 3)
+
+
+# ---- rms_norm / softmax plan instructions (host side: lowering and the oracle's restatement) ----------
+
+
+def test_rms_norm_and_softmax_lower_to_the_reference_kernel_names():
+    import struct
+    gb = GraphBuilder()
+    x = gb.input(["batch", 8])
+    w = gb.constant(np.linspace(0.5, 1.5, 8, dtype=np.float32).tobytes(), TensorType.new([8]))
+    y = gb.softmax(gb.rms_norm(x, w, 1e-6), -1)
+    graph = gb.to_graph()
+    graph.inputs, graph.outputs = gb.recorded_input_ids(), [y.node_id()]
+    mp = plan_memory(graph)
+    plan = lower_to_plan(graph, mp)
+    calls = [i for i in plan.instructions if isinstance(i, CallKernel)]
+    assert [c.kernel_name for c in calls] == ["rms_norm", "softmax"]
+    assert calls[0].params[0] == struct.unpack("<I", struct.pack("<f", 1e-6))[0]   # eps as f32 bits
+    assert calls[0].params[1] == 8 and len(calls[0].input_slices) == 2
+    assert calls[1].params == [8, 1] and calls[1].param_dims[:2] == [8, 1]
+
+
+def test_softmax_stride_for_an_inner_axis():
+    gb = GraphBuilder()
+    x = gb.input([2, 5, 3])
+    y = gb.softmax(x, 1)
+    graph = gb.to_graph()
+    graph.inputs, graph.outputs = gb.recorded_input_ids(), [y.node_id()]
+    plan = lower_to_plan(graph, plan_memory(graph))
+    call = [i for i in plan.instructions if isinstance(i, CallKernel)][0]
+    assert call.params == [5, 3]
+
+
+def test_oracle_rms_norm_matches_the_reference_fused_test_vector():
+    """tests/residual_add_norm.rs:327-355 (hidden row size 4, batch 2): x = main + residual."""
+    import oracle as orc
+    main = np.array([1.0, -2.0, 3.5, -4.5, 2.25, -1.0, 0.5, 3.0], np.float32)
+    residual = np.array([-0.25, 0.5, -1.5, 2.0, 1.25, -0.75, 2.5, -3.5], np.float32)
+    weight = np.array([0.75, -1.25, 1.5, 0.5], np.float32)
+    x = (main + residual).reshape(2, 4)
+    want = x / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-5) * weight
+    got = orc.rms_norm(x, weight, 1e-5)
+    assert np.allclose(got, want, rtol=0, atol=1e-5)
+    # the unfused dispatch arm as written takes rows of len / w_len = 2 elements instead
+    as_written = orc.rms_norm(x, weight, 1e-5, orc.MODE_AS_WRITTEN)
+    assert not np.allclose(as_written, want, atol=1e-3)
+
+
+def test_oracle_softmax_rows_sum_to_one_on_any_axis():
+    import oracle as orc
+    x = np.random.default_rng(3).standard_normal((2, 5, 3)).astype(np.float32) * 4
+    for axis in (0, 1, 2, -1):
+        s = orc.softmax(x, axis)
+        e = np.exp(x - x.max(axis, keepdims=True))
+        assert np.allclose(s, e / e.sum(axis, keepdims=True), atol=1e-6)
+        assert np.allclose(s.sum(axis), 1.0, atol=1e-5)
