@@ -62,6 +62,8 @@ SIGNATURES = {
                                        _sz]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_rms_norm": (_int, [_vp, _vp, _sz, _sz, _c.c_longlong, _sz, _sz, _c.c_float, _sz]),
+    "fnn_cuda_row_norm": (_int, [_vp, _vp, _int, _sz, _sz, _c.c_longlong, _c.c_longlong, _sz, _c.c_longlong, _sz,
+                                 _sz, _c.c_float, _sz]),
     "fnn_cuda_softmax": (_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_memcpy": (_int, [_vp, _vp, _sz, _sz, _sz]),
     "fnn_cuda_fill": (_int, [_vp, _vp, _sz, _sz, _f]),

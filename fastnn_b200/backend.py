@@ -374,17 +374,30 @@ class CudaBackend:
                                             a.size // 4, b.offset, b.size // 4,
                                             instr.output_slice.offset, out_len))
             return
-        if name == "rms_norm":
-            data, weight = instr.input_slices[0], instr.input_slices[1]
+        if name in ("rms_norm", "norm_f32", "fused_residual_add_rms_norm", "fused_residual_add_layer_norm"):
+            sl = list(instr.input_slices)
+            fused = name.startswith("fused_residual_add_")
+            residual = sl.pop(0) if fused else None          # fused: [residual, main, weight, bias]
+            data = sl.pop(0)
+            weight = sl.pop(0) if sl else None
+            bias = sl.pop(0) if sl else None
+            if name == "norm_f32" and len(instr.params) > 1 and instr.params[1] == 1:
+                raise BackendError("UnsupportedOp", "batch norm is not on the CUDA backend's path")
             n = instr.output_slice.size // 4
             if instr.param_dims:
                 n = 1
                 for d in instr.param_dims:
                     n *= env.resolve(d)
             eps = struct.unpack("<f", struct.pack("<I", instr.params[0] & 0xFFFFFFFF))[0]
-            hidden = instr.params[1] if len(instr.params) > 1 and instr.params[1] > 0 else weight.size // 4
-            _check(lib.fnn_cuda_rms_norm(self.ctx, arena.handle, data.offset, n, weight.offset,
-                                         weight.size // 4, hidden, eps, instr.output_slice.offset))
+            row_idx = 2 if name == "norm_f32" else 1
+            row = instr.params[row_idx] if len(instr.params) > row_idx and instr.params[row_idx] > 0 else \
+                (weight.size // 4 if weight is not None else n)
+            kind = 0 if name.endswith("rms_norm") else 1
+            _check(lib.fnn_cuda_row_norm(
+                self.ctx, arena.handle, kind, data.offset, n, residual.offset if residual else -1,
+                weight.offset if weight else -1, weight.size // 4 if weight else 0,
+                bias.offset if bias else -1, bias.size // 4 if bias else 0, row, eps,
+                instr.output_slice.offset))
             return
         if name == "softmax":
             src = instr.input_slices[0]

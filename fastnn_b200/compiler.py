@@ -7,7 +7,7 @@ It mirrors, by name and behaviour, the reference call stack
 fusion, weight quantization, memory planning, ``backend.compile``) ->
 ``GraphExecutor::execute`` (src/backend/executor.rs:599-858), and the Python entry
 ``AotExecutor`` (src/python/nn.rs:1219-1431).  Only the opcodes on the path exist here:
-Input, Constant, MatMul, Add/Sub/Mul, Relu/Gelu/Silu, RMSNorm, Softmax.
+Input, Constant, MatMul, Add/Sub/Mul, Relu/Gelu/Silu, RMSNorm, LayerNorm, Softmax.
 
 The heavy lifting is not here: quantization calls the library's host pass
 (``fnn_quantize_weights``) and every plan instruction runs as a CUDA kernel.
@@ -40,6 +40,7 @@ class Opcode(enum.Enum):
     Gelu = "Gelu"
     Silu = "Silu"
     RMSNorm = "RMSNorm"
+    LayerNorm = "LayerNorm"
     Softmax = "Softmax"
 
 
@@ -263,6 +264,16 @@ class GraphBuilder:
         node.attrs["eps"] = repr(float(eps))
         return GraphTensor(self, node.id)
 
+    def layer_norm(self, x: GraphTensor, weight: GraphTensor, bias: GraphTensor,
+                   eps: float = 1e-5) -> GraphTensor:
+        """src/ir/builder.rs:1095-1117: LayerNorm(input, weight, bias), attributes `eps` and
+        `normalized_ndims` (rank of the weight)."""
+        node = self.graph.add(Opcode.LayerNorm, [x.node_id(), weight.node_id(), bias.node_id()],
+                              TensorType.new(x.shape()))
+        node.attrs["eps"] = repr(float(eps))
+        node.attrs["normalized_ndims"] = str(len(weight.shape()))
+        return GraphTensor(self, node.id)
+
     def softmax(self, x: GraphTensor, dim: int = -1) -> GraphTensor:
         """src/ir/builder.rs:816-828: Softmax with attribute `axis`."""
         node = self.graph.add(Opcode.Softmax, [x.node_id()], TensorType.new(x.shape()))
@@ -459,7 +470,7 @@ def plan_memory(graph: ComputeGraph) -> MemoryPlan:
     free: List[Slot] = []
     top = 0
     elementwise = (Opcode.Add, Opcode.Sub, Opcode.Mul, Opcode.Relu, Opcode.Gelu, Opcode.Silu,
-                   Opcode.RMSNorm, Opcode.Softmax)   # both row kernels work in place
+                   Opcode.RMSNorm, Opcode.LayerNorm, Opcode.Softmax)   # the row kernels work in place
     for step, n in enumerate(order):
         size = max(n.output_type.byte_size(), 4)
         padded = -(-size // _ALIGN) * _ALIGN
@@ -530,6 +541,19 @@ def lower_to_plan(graph: ComputeGraph, memory_plan: MemoryPlan) -> ExecutablePla
                 instructions.append(WriteConst(out, n.value))
             else:
                 instructions.append(Fill(out, float(n.value)))
+    # Add -> RMSNorm / LayerNorm with the Add consumed by nothing else becomes one fused row kernel, as
+    # the reference's residual-add-norm fusion does (FusedResidualAddNorm, src/ir/node.rs:136-138;
+    # kernels "fused_residual_add_{rms_norm,layer_norm}", src/backend/cpu/mod.rs:2424-2500)
+    fused_norm: Dict[int, Tuple[int, int]] = {}
+    for n in order:
+        if n.opcode in (Opcode.RMSNorm, Opcode.LayerNorm):
+            add = graph.get_node(n.inputs[0])
+            if (add.opcode == Opcode.Add and "fused_op" not in add.attrs and add.id not in graph.outputs
+                    and graph.consumers(add.id) == [n.id] and len(add.inputs) == 2):
+                a0, a1 = (graph.get_node(i) for i in add.inputs)
+                if list(a0.output_type.shape) == list(a1.output_type.shape) == list(n.output_type.shape):
+                    fused_norm[n.id] = (add.inputs[0], add.inputs[1])
+                    skip.add(add.id)
     for n in order:
         if n.id in skip:
             continue
@@ -599,14 +623,25 @@ def lower_to_plan(graph: ComputeGraph, memory_plan: MemoryPlan) -> ExecutablePla
                                            [_slice(memory_plan, i) for i in n.inputs], out, [],
                                            node_id=n.id, param_dims=list(n.output_type.shape)))
             continue
-        if n.opcode == Opcode.RMSNorm:
-            # kernel "rms_norm", params [eps bits] (src/backend/cpu/mod.rs:1526-1545); params[1] carries
-            # the hidden size so that batched inputs normalise rows of weight-length
+        if n.opcode in (Opcode.RMSNorm, Opcode.LayerNorm):
+            # "rms_norm" params [eps bits] (src/backend/cpu/mod.rs:1526-1545), "norm_f32" params
+            # [eps bits, is_batch_norm = 0] (:980-1001), "fused_residual_add_*" params [eps bits, row size]
+            # with inputs [residual, main, weight, bias] (:2424-2500).  The row size (weight length) rides
+            # along in every case so that batched inputs normalise rows of the hidden size.
             eps = float(n.attrs.get("eps", "1e-5"))
-            hidden = graph.get_node(n.inputs[1]).output_type.numel_max()
+            hidden = int(graph.get_node(n.inputs[1]).output_type.numel_max())
             bits = struct.unpack("<I", struct.pack("<f", eps))[0]
-            instructions.append(CallKernel("rms_norm", [_slice(memory_plan, i) for i in n.inputs], out,
-                                           [bits, int(hidden)], node_id=n.id,
+            rms = n.opcode == Opcode.RMSNorm
+            if n.id in fused_norm:
+                main, residual = fused_norm[n.id]
+                slices = [_slice(memory_plan, residual), _slice(memory_plan, main)] + \
+                         [_slice(memory_plan, i) for i in n.inputs[1:]]
+                name = "fused_residual_add_rms_norm" if rms else "fused_residual_add_layer_norm"
+                params = [bits, hidden]
+            else:
+                slices = [_slice(memory_plan, i) for i in n.inputs]
+                name, params = ("rms_norm", [bits, hidden]) if rms else ("norm_f32", [bits, 0, hidden])
+            instructions.append(CallKernel(name, slices, out, params, node_id=n.id,
                                            param_dims=list(n.output_type.shape)))
             continue
         if n.opcode == Opcode.Softmax:
@@ -791,7 +826,7 @@ class AotExecutor:
     """Python-facing executor with the constructor of fastnn's `AotExecutor`
     (src/python/nn.rs:1221-1364): ONNX-style node dicts + a parameter dict.  `params` become
     `Constant` nodes (src/onnx/converter.rs:114-133), `Gemm` lowers to matmul (+ add)
-    (:290-318).  Supported op_types: MatMul, Gemm (transB = 0), Add, Relu, Gelu, Silu, RMSNorm, Softmax."""
+    (:290-318).  Supported op_types: MatMul, Gemm (transB = 0), Add, Relu, Gelu, Silu, RMSNorm, LayerNorm, Softmax."""
 
     def __init__(self, nodes: Sequence[Dict[str, object]], params: Dict[str, np.ndarray],
                  input_names: Sequence[str], output_names: Sequence[str],
@@ -838,6 +873,8 @@ class AotExecutor:
                 r = gb.silu(t[0])
             elif op in ("RMSNorm", "RmsNorm", "SimplifiedLayerNormalization"):
                 r = gb.rms_norm(t[0], t[1], float(nd.get("eps", nd.get("epsilon", 1e-5))))
+            elif op in ("LayerNorm", "LayerNormalization"):
+                r = gb.layer_norm(t[0], t[1], t[2], float(nd.get("eps", nd.get("epsilon", 1e-5))))
             elif op == "Softmax":
                 r = gb.softmax(t[0], int(nd.get("axis", -1)))
             else:

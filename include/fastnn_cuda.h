@@ -224,6 +224,13 @@ int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_
  * (src/backend/cpu/mod.rs:5053-5075).  out may be in. */
 int fnn_cuda_rms_norm(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t in_offset, size_t len,
                       long long w_offset, size_t w_len, size_t row_size, float eps, size_t out_offset);
+/* The general row normalisation behind "rms_norm", "fused_residual_add_rms_norm" and
+ * "fused_residual_add_layer_norm" (src/backend/cpu/mod.rs:2424-2500, 5053-5230): kind 0 = rms_norm,
+ * 1 = layer_norm with population variance; x = in + residual when res_offset >= 0; weight and bias are
+ * optional (offset < 0), default 1 and 0 (src/backend/cpu/microkernels/ops.rs:788-825, 1012-1044). */
+int fnn_cuda_row_norm(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, int kind, size_t in_offset, size_t len,
+                      long long res_offset, long long w_offset, size_t w_len, long long b_offset,
+                      size_t b_len, size_t row_size, float eps, size_t out_offset);
 /* softmax along an axis of axis_dim elements that are `stride` floats apart; len / axis_dim rows
  * (kernel "softmax", params [axis_dim, stride]: src/backend/cpu/mod.rs:1002-1050, 3488-3514;
  * src/backend/cpu/microkernels/ops.rs:1363-1397).  out may be in. */

@@ -85,6 +85,8 @@ def lib() -> ctypes.CDLL:
     L.orc_add_broadcast.restype = None
     L.orc_rms_norm.argtypes = [c_vp, c_sz, c_vp, c_sz, c_sz, ctypes.c_float, c_vp]
     L.orc_rms_norm.restype = None
+    L.orc_layer_norm.argtypes = [c_vp, c_vp, c_sz, c_vp, c_sz, c_vp, c_sz, c_sz, ctypes.c_float, c_vp]
+    L.orc_layer_norm.restype = None
     L.orc_softmax.argtypes = [c_vp, c_sz, c_sz, c_sz, c_vp]
     L.orc_softmax.restype = None
     L.orc_simd_level.restype = c_int
@@ -283,6 +285,20 @@ def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float, mode: int = MODE_INT
     out = np.empty(x.size, dtype=np.float32)
     lib().orc_rms_norm(_p(x.reshape(-1)), x.size, _p(weight) if weight.size else None, weight.size,
                        row, ctypes.c_float(eps), _p(out))
+    return out.reshape(x.shape)
+
+
+def layer_norm(x: np.ndarray, weight, bias, eps: float, residual=None) -> np.ndarray:
+    """Rows of the last dimension; x + residual is normalised when a residual is given."""
+    x = _f32(x)
+    row = x.shape[-1]
+    w = _f32(weight).reshape(-1) if weight is not None else np.zeros(0, np.float32)
+    b = _f32(bias).reshape(-1) if bias is not None else np.zeros(0, np.float32)
+    r = _f32(residual).reshape(-1) if residual is not None else None
+    out = np.empty(x.size, dtype=np.float32)
+    lib().orc_layer_norm(_p(x.reshape(-1)), _p(r) if r is not None else None, x.size,
+                         _p(w) if w.size else None, w.size, _p(b) if b.size else None, b.size, row,
+                         ctypes.c_float(eps), _p(out))
     return out.reshape(x.shape)
 
 

@@ -644,6 +644,34 @@ void orc_rms_norm(const float *in, size_t n, const float *w, size_t w_len, size_
     }
 }
 
+/* src/backend/cpu/microkernels/ops.rs:788-825 (fused_residual_add_layer_norm_f32_scalar). */
+void orc_layer_norm(const float *in, const float *residual, size_t n, const float *w, size_t w_len,
+                    const float *b, size_t b_len, size_t row_size, float eps, float *out) {
+    if (row_size == 0) return;
+    size_t rows = n / row_size;
+    for (size_t r = 0; r < rows; ++r) {
+        size_t s0 = r * row_size;
+        float mean = 0.0f, m2 = 0.0f;
+        unsigned count = 0;
+        for (size_t i = 0; i < row_size; ++i) {
+            count += 1;
+            float x = residual ? in[s0 + i] + residual[s0 + i] : in[s0 + i];
+            float delta = x - mean;
+            mean += delta / (float)count;
+            float delta2 = x - mean;
+            m2 += delta * delta2;
+        }
+        float var = count > 1 ? m2 / (float)count : 0.0f;
+        float inv_std = 1.0f / sqrtf(var + eps);
+        for (size_t i = 0; i < row_size; ++i) {
+            float x = residual ? in[s0 + i] + residual[s0 + i] : in[s0 + i];
+            float wi = i < w_len ? w[i] : 1.0f;
+            float bi = i < b_len ? b[i] : 0.0f;
+            out[s0 + i] = (x - mean) * inv_std * wi + bi;
+        }
+    }
+}
+
 /* src/backend/cpu/microkernels/ops.rs:1363-1397 (softmax_f32_scalar_strided). */
 void orc_softmax(const float *in, size_t n, size_t axis_dim, size_t stride, float *out) {
     if (axis_dim == 0) axis_dim = 1;

@@ -99,6 +99,12 @@ void orc_add_broadcast(const float *a, size_t a_len, const float *b, size_t b_le
 void orc_rms_norm(const float *in, size_t n, const float *w, size_t w_len, size_t row_size, float eps,
                   float *out);
 
+/* fused_residual_add_layer_norm: x = main + residual per element, Welford mean / population variance
+ * per row, out = (x - mean) * (1 / sqrt(var + eps)) * w[i] + b[i]; residual, w, b may be NULL
+ * (w = 1, b = 0).  src/backend/cpu/microkernels/ops.rs:788-825. */
+void orc_layer_norm(const float *in, const float *residual, size_t n, const float *w, size_t w_len,
+                    const float *b, size_t b_len, size_t row_size, float eps, float *out);
+
 /* softmax plan instruction over the axis of size axis_dim whose elements are `stride` apart;
  * n / axis_dim rows.  src/backend/cpu/microkernels/ops.rs:1363-1397. */
 void orc_softmax(const float *in, size_t n, size_t axis_dim, size_t stride, float *out);

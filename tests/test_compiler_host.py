@@ -243,3 +243,50 @@ def test_oracle_softmax_rows_sum_to_one_on_any_axis():
         e = np.exp(x - x.max(axis, keepdims=True))
         assert np.allclose(s, e / e.sum(axis, keepdims=True), atol=1e-6)
         assert np.allclose(s.sum(axis), 1.0, atol=1e-5)
+
+
+def test_add_feeding_a_norm_becomes_the_fused_residual_kernel():
+    """Kernel names and input order [residual, main, weight, bias] of the reference's
+    FusedResidualAddNorm lowering (src/backend/cpu/mod.rs:2424-2500)."""
+    for norm in ("rms", "layer"):
+        gb = GraphBuilder()
+        main, res = gb.input([2, 4]), gb.input([2, 4])
+        w = gb.constant(np.ones(4, np.float32).tobytes(), TensorType.new([4]))
+        b = gb.constant(np.zeros(4, np.float32).tobytes(), TensorType.new([4]))
+        s = gb.add(main, res)
+        y = gb.rms_norm(s, w, 1e-5) if norm == "rms" else gb.layer_norm(s, w, b, 1e-5)
+        graph = gb.to_graph()
+        graph.inputs, graph.outputs = gb.recorded_input_ids(), [y.node_id()]
+        mp = plan_memory(graph)
+        calls = [i for i in lower_to_plan(graph, mp).instructions if isinstance(i, CallKernel)]
+        assert [c.kernel_name for c in calls] == [f"fused_residual_add_{norm}_norm"]
+        assert len(calls[0].input_slices) == (3 if norm == "rms" else 4)
+        assert calls[0].params[1] == 4
+        # residual first, main second
+        assert calls[0].input_slices[0].offset == mp.slots[res.node_id()].offset
+        assert calls[0].input_slices[1].offset == mp.slots[main.node_id()].offset
+
+
+def test_layer_norm_alone_lowers_to_norm_f32():
+    gb = GraphBuilder()
+    x = gb.input([3, 8])
+    w = gb.constant(np.ones(8, np.float32).tobytes(), TensorType.new([8]))
+    b = gb.constant(np.zeros(8, np.float32).tobytes(), TensorType.new([8]))
+    y = gb.layer_norm(x, w, b, 1e-5)
+    graph = gb.to_graph()
+    graph.inputs, graph.outputs = gb.recorded_input_ids(), [y.node_id()]
+    calls = [i for i in lower_to_plan(graph, plan_memory(graph)).instructions if isinstance(i, CallKernel)]
+    assert calls[0].kernel_name == "norm_f32" and calls[0].params[1] == 0 and calls[0].params[2] == 8
+
+
+def test_oracle_layer_norm_matches_the_reference_fused_test_vector():
+    """tests/residual_add_norm.rs:357-390: main + residual, weight and bias of length 4."""
+    import oracle as orc
+    main = np.array([0.5, -1.0, 2.0, -3.0, 1.5, 2.5, -0.75, -1.25], np.float32).reshape(2, 4)
+    residual = np.array([1.0, 0.25, -0.5, 1.75, -2.0, 0.5, 1.25, -0.25], np.float32).reshape(2, 4)
+    weight = np.array([1.25, 0.75, -0.5, 1.5], np.float32)
+    bias = np.array([0.1, -0.2, 0.3, -0.4], np.float32)
+    x = (main + residual).astype(np.float64)
+    want = (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5) * weight + bias
+    got = orc.layer_norm(main, weight, bias, 1e-5, residual)
+    assert np.allclose(got, want, atol=1e-5)

@@ -110,3 +110,49 @@ def test_aot_executor_accepts_rms_norm_and_softmax_nodes(backend):
     got = ex.forward({"x": x})["y"]
     a = orc.qmatmul(orc.quantize_kn(orc.FMT_I8, w), orc.rms_norm(x, g, 1e-5))
     assert max_err_vs_rms(got, orc.softmax(a, -1)) <= 2e-3
+
+
+@pytest.mark.parametrize("kind", ["rms", "layer"])
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (7, 1000), (3, 5)])
+def test_row_norm_with_residual_matches_oracle(backend, kind, rows, hidden):
+    """fnn_cuda_row_norm: x = in + residual, then rms_norm or layer_norm with weight (and bias)."""
+    x, r = normal(750 + hidden, (rows, hidden), 1.5), normal(751 + hidden, (rows, hidden), 0.7)
+    w, b = normal(752 + hidden, (hidden,), 1.0), normal(753 + hidden, (hidden,), 0.2)
+    al = lambda v: -(-v // 256) * 256
+    offs, top = {}, 0
+    for name, arr in (("x", x), ("r", r), ("w", w), ("b", b), ("y", x)):
+        offs[name], top = top, top + al(arr.nbytes)
+    arena = backend.allocate_arena(top)
+    try:
+        for name, arr in (("x", x), ("r", r), ("w", w), ("b", b)):
+            backend.write_arena(arena, offs[name], arr.tobytes())
+        k = 0 if kind == "rms" else 1
+        _check(backend.lib.fnn_cuda_row_norm(backend.ctx, arena.handle, k, offs["x"], x.size, offs["r"],
+                                             offs["w"], hidden, offs["b"] if k else -1, hidden if k else 0,
+                                             hidden, 1e-5, offs["y"]))
+        backend.synchronize()
+        got = np.frombuffer(backend.read_arena(arena, offs["y"], x.nbytes), np.float32).reshape(x.shape)
+    finally:
+        arena.close()
+    want = orc.rms_norm(x + r, w, 1e-5) if kind == "rms" else orc.layer_norm(x, w, b, 1e-5, r)
+    assert np.allclose(got, want, rtol=1e-4, atol=2e-6), np.abs(got - want).max()
+
+
+def test_residual_block_through_the_graph_builder(backend):
+    """h = x + W_o(a); y = W_up(layer_norm(h)) with GELU: the Add feeds the norm and is fused into it."""
+    m, k, n = 4, 512, 768
+    x, a = normal(760, (m, k), 1.0), normal(761, (m, k), 1.0)
+    wo, wu = normal(762, (k, k), 0.04), normal(763, (k, n), 0.04)
+    g, beta = np.abs(normal(764, (k,), 1.0)) + 0.5, normal(765, (k,), 0.1)
+    gb = GraphBuilder()
+    xi, ai = gb.input_with_dims([m, k]), gb.input_with_dims([m, k])
+    h = gb.add(xi, gb.matmul(ai, gb.constant(wo, TensorType.new([k, k]))))
+    t = gb.layer_norm(h, gb.constant(g.tobytes(), TensorType.new([k])),
+                      gb.constant(beta.tobytes(), TensorType.new([k])), 1e-5)
+    y = gb.gelu(gb.matmul(t, gb.constant(wu, TensorType.new([k, n]))))
+    out = gb.compile_and_execute_with_quantize([y], backend, [x.tobytes(), a.tobytes()], 8)
+    got = np.frombuffer(out[0], np.float32).reshape(m, n)
+    o = orc.qmatmul(orc.quantize_kn(orc.FMT_I8, wo), a)
+    ln = orc.layer_norm(x, g, beta, 1e-5, o)
+    want = orc.qmatmul(orc.quantize_kn(orc.FMT_I8, wu), ln, None, orc.EPI_GELU)
+    assert max_err_vs_rms(got, want) <= 2e-3
