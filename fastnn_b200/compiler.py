@@ -464,6 +464,13 @@ def plan_memory(graph: ComputeGraph) -> MemoryPlan:
     for step, n in enumerate(order):
         for i in n.inputs:
             last_use[i] = step
+        # a norm may absorb the Add in front of it at lowering time and then reads the Add's operands
+        # itself: they stay alive until the norm
+        if n.opcode in (Opcode.RMSNorm, Opcode.LayerNorm):
+            src = graph.get_node(n.inputs[0])
+            if src.opcode == Opcode.Add:
+                for i in src.inputs:
+                    last_use[i] = step
     persistent = set(graph.outputs) | set(graph.inputs)
     persistent |= {n.id for n in order if n.opcode == Opcode.Constant}
     slots: Dict[int, Slot] = {}
