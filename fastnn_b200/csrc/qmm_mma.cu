@@ -196,13 +196,12 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // One block per SM.  Its G groups of 8 warps share the staged activations; each group streams
 // its own row tiles, splitting K across its warps.
-template <int FMT, int CG>
-__global__ void __launch_bounds__(groups_for(FMT, CG) * kW * 32, 1)
+template <int FMT, int CG, int G>
+__global__ void __launch_bounds__(G * kW * 32, 1)
 qmm_mma_kernel(MmaParams p) {
     using T = FragTraits<FMT>;
     constexpr int KBLK = T::KBLK, VEC = T::VEC;
     constexpr int COLS = 8 * CG;
-    constexpr int G = groups_for(FMT, CG);
     constexpr int NT = G * kW * 32;   // threads per block
     constexpr int NW = G * kW;        // warps per block
     constexpr int S = stages_for(CG);
@@ -573,10 +572,9 @@ int ensure_frag(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
     return FNN_OK;
 }
 
-template <int FMT, int CG>
-int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out, int M, int split) {
+template <int FMT, int CG, int G>
+int launch_mma_g(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out, int M, int split) {
     using T = FragTraits<FMT>;
-    constexpr int G = groups_for(FMT, CG);
     const fnn_cuda_qweight *w = a.w;
     MmaParams p{};
     p.frag = w->frag;
@@ -629,12 +627,27 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
     p.Kc = Kc;
     const size_t act_bytes = (size_t)act_rows * (2 * Kc + T::PAD_BYTES);
     const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
-    auto kern = qmm_mma_kernel<FMT, CG>;
+    auto kern = qmm_mma_kernel<FMT, CG, G>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(kern, grid, G * kW * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     return FNN_OK;
+}
+
+// Groups per block: the most the register and shared-memory budget allows (groups_for) while that
+// still gives (nearly) every SM a block; for the single-column-group kernels, layers with fewer row
+// tiles run fewer groups per block so that the tiles spread over more SMs.
+template <int FMT, int CG>
+int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out, int M, int split) {
+    constexpr int GMAX = groups_for(FMT, CG);
+    if (CG == 1) {
+        const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
+        if (GMAX >= 3 && (ntiles + 2) / 3 >= want) return launch_mma_g<FMT, CG, GMAX>(ctx, a, act, out, M, split);
+        if ((ntiles + 1) / 2 >= want) return launch_mma_g<FMT, CG, (GMAX < 2 ? GMAX : 2)>(ctx, a, act, out, M, split);
+        return launch_mma_g<FMT, CG, 1>(ctx, a, act, out, M, split);
+    }
+    return launch_mma_g<FMT, CG, GMAX>(ctx, a, act, out, M, split);
 }
 
 template <int FMT>

@@ -1,4 +1,4 @@
-// Skinny-M kernel (1 <= M <= 8) on 8-bit tensor-core operands: the HBM scan of the weights with
+// Skinny-M kernel (1 <= M <= 4) on 8-bit tensor-core operands: the HBM scan of the weights with
 // almost no instruction per weight.
 //
 // Same skeleton as the fp16 fragment kernel (fragment-major weights, one block per SM, groups of
@@ -27,7 +27,7 @@ namespace {
 constexpr int kW8 = 8;   // warps per group
 constexpr int kU8 = 2;   // k-blocks per ring chunk
 constexpr int kS8 = 3;   // ring stages per lane (two chunks, 96 KB per SM, in flight)
-constexpr int kG8 = 3;   // groups per block
+constexpr int kG8Max = 3;   // groups per block (fewer when a layer has too few row tiles to fill the SMs)
 
 template <int FMT>
 struct T8 {
@@ -125,7 +125,7 @@ struct P8 {
     GatherArgs g;
 };
 
-template <int FMT, int CG>
+template <int FMT, int CG, int kG8>
 __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
 qmm_mma8_kernel(P8 p) {
     using TT = T8<FMT>;
@@ -436,7 +436,7 @@ qmm_mma8_kernel(P8 p) {
     if (p.gather_on) gather_finish(p.g, step, p.M, p.N);
 }
 
-template <int FMT, int CG>
+template <int FMT, int CG, int kG8>
 int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
     using TT = T8<FMT>;
     const fnn_cuda_qweight *w = a.w;
@@ -484,7 +484,7 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
     p.Kc = Kc;
     const size_t act_bytes = (((size_t)cols * (Kc + TT::PAD)) + 15) & ~(size_t)15;
     const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
-    auto kern = qmm_mma8_kernel<FMT, CG>;
+    auto kern = qmm_mma8_kernel<FMT, CG, kG8>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(kern, grid, kG8 * kW8 * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
@@ -498,7 +498,14 @@ int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const int M = (int)a.M;
     // int8 pairs always; e4m3 triples while they fit one 8-column group with the batch, pairs beyond
     const int T = T8<FMT>::is_int ? 2 : (M <= 2 ? 3 : 2);
-    return (T * M <= 8) ? launch8<FMT, 1>(ctx, a, T) : launch8<FMT, 2>(ctx, a, T);
+    FNN_REQUIRE(T * M <= 8, FNN_ERR_UNSUPPORTED,
+                "qmatmul: the 8-bit fragment kernel holds one 8-column group (M=%d, %d terms)", M, T);
+    // Groups per block: three while that still gives (nearly) every SM a block; layers with fewer row
+    // tiles run two or one group per block so that the tiles spread over more SMs.
+    const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
+    if ((ntiles + 2) / 3 >= want) return launch8<FMT, 1, 3>(ctx, a, T);
+    if ((ntiles + 1) / 2 >= want) return launch8<FMT, 1, 2>(ctx, a, T);
+    return launch8<FMT, 1, 1>(ctx, a, T);
 }
 
 }  // namespace
