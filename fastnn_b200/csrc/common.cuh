@@ -90,10 +90,12 @@ struct fnn_cuda_qweight {
     size_t frag_bytes = 0;
     float *frag_bs = nullptr;   // I4CB block scales in fragment order
     bool mma_ok = true;         // false when values would leave the fp16 range of that kernel
-    // tile-major copy for the tcgen05 kernel (built on demand)
+    // tile-major operand copy for the tcgen05 kernel (built on demand): [row tile of 128][K block of
+    // 128 bytes][128 rows][128 bytes], zero padded, so that every TMA box is 16 KB of contiguous memory.
+    // One byte per weight (8-bit codes as stored, I4 -> int8, FP4 -> e4m3) or fp16 (codebook format).
     void *tc = nullptr;
     size_t tc_bytes = 0;
-    size_t tc_ld = 0;           // row stride of the byte-expanded copy
+    size_t tc_kblocks = 0;      // K blocks per row tile
     int tc_kind = 0;
 };
 

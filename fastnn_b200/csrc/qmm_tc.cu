@@ -86,6 +86,13 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+// Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
                                             int c1, int c2) {
     asm volatile(
@@ -245,6 +252,8 @@ struct TcParams {
     int Mb;        // batch rows per tile
     int n_tiles, m_tiles;
     int kblocks;   // ceil(K / 128)
+    int tiled;     // weights come from the tile-major copy (one contiguous, pre-swizzled 16 KB per stage)
+    const unsigned char *w_tiles;
     int stages;
     int epilogue;
 };
@@ -315,7 +324,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         break;
                     }
                     mbar_expect_tx(&full[s], (uint32_t)(a_bytes + b_bytes));
-                    tma_load_2d(s_a + (size_t)s * a_bytes, &map_w, &full[s], kb * kKBlockBytes, nt * kTileN);
+                    if (p.tiled)
+                        bulk_load(s_a + (size_t)s * a_bytes,
+                                  p.w_tiles + (size_t)(nt * p.kblocks + kb) * a_bytes, a_bytes, &full[s]);
+                    else
+                        tma_load_2d(s_a + (size_t)s * a_bytes, &map_w, &full[s], kb * kKBlockBytes, nt * kTileN);
                     tma_load_3d(s_b + (size_t)s * b_stride, &map_a, &full[s], kb * kKBlockBytes, mt * p.Mb, 0);
                     if (++s == p.stages) {
                         s = 0;
@@ -464,6 +477,23 @@ int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, c
     return FNN_OK;
 }
 
+// Tensor map of the weight operand.  With the tile-major copy the tensor is [tiles * K blocks * 128
+// rows][128 bytes] and the box of (row tile nt, K block kb) starts at row (nt * kblocks + kb) * 128:
+// 16 KB of contiguous memory.  Without it (8-bit codes that were never prepared) the rows are read in
+// place, 128 bytes from each of 128 rows.
+int encode_weight_map(CUtensorMap *map, const fnn_cuda_qweight *w, int Kbytes) {
+    cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
+    if (w->tc) {
+        const size_t n_tiles = div_ceil(w->N, (size_t)kTileN);
+        cuuint64_t dims[2] = {(cuuint64_t)kKBlockBytes, (cuuint64_t)(n_tiles * w->tc_kblocks * kTileN)};
+        cuuint64_t strides[1] = {(cuuint64_t)kKBlockBytes};
+        return encode_map(map, w->tc, 2, dims, strides, box);
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)Kbytes, (cuuint64_t)w->N};
+    cuuint64_t strides[1] = {(cuuint64_t)w->ld_u4 * 16};
+    return encode_map(map, (void *)w->rows, 2, dims, strides, box);
+}
+
 template <int KIND, int T>
 int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const fnn_cuda_qweight *w = a.w;
@@ -495,12 +525,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 
     CUtensorMap map_w, map_a;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)Kbytes, (cuuint64_t)N};
-        // 8-bit codes are read in place; 4-bit codes from their byte-expanded copy
-        void *base = w->tc ? w->tc : (void *)w->rows;
-        cuuint64_t strides[1] = {w->tc ? (cuuint64_t)w->tc_ld : (cuuint64_t)w->ld_u4 * 16};
-        cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
-        rc = encode_map(&map_w, base, 2, dims, strides, box);
+        rc = encode_weight_map(&map_w, w, Kbytes);
         if (rc != FNN_OK) return rc;
     }
     {
@@ -526,6 +551,8 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     p.n_tiles = (N + kTileN - 1) / kTileN;
     p.m_tiles = m_tiles;
     p.kblocks = (Kbytes + kKBlockBytes - 1) / kKBlockBytes;
+    p.tiled = w->tc != nullptr;
+    p.w_tiles = (const unsigned char *)w->tc;
     p.epilogue = a.epilogue;
     const int a_bytes = kTileN * kKBlockBytes;
     const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
@@ -578,12 +605,7 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
 
     CUtensorMap map_w, map_a;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
-        // 8-bit codes are read in place; 4-bit codes from their byte-expanded copy
-        void *base = w->tc ? w->tc : (void *)w->rows;
-        cuuint64_t strides[1] = {w->tc ? (cuuint64_t)w->tc_ld : (cuuint64_t)w->ld_u4 * 16};
-        cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
-        rc = encode_map(&map_w, base, 2, dims, strides, box);
+        rc = encode_weight_map(&map_w, w, K);
         if (rc != FNN_OK) return rc;
     }
     {
@@ -609,6 +631,8 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
     p.n_tiles = (N + kTileN - 1) / kTileN;
     p.m_tiles = m_tiles;
     p.kblocks = (K + kKBlockBytes - 1) / kKBlockBytes;
+    p.tiled = w->tc != nullptr;
+    p.w_tiles = (const unsigned char *)w->tc;
     p.epilogue = a.epilogue;
     const int a_bytes = kTileN * kKBlockBytes;
     const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
@@ -627,16 +651,42 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
 }
 
 
-// Codebook weights -> fp16 of blockscale * centroid (one rounding), [N][ld bytes], for kind::f16.
-__global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
-                                       const float *bscales, size_t bpr, const float *codebook, size_t ld,
-                                       __half *out) {
-    const size_t ldh = ld / 2, total = N * ldh;
+// Position i of the tile-major copy -> (weight row n, byte offset inside the row's operand bytes).
+// Each 16 KB tile is stored the way the 128-byte swizzle lays it out in shared memory (16-byte chunk
+// index XOR row mod 8), so that one untiled bulk copy of 16 KB brings it in ready for the MMA.
+__device__ __forceinline__ void tile_pos(size_t i, size_t kblocks, size_t &n, size_t &byte) {
+    const size_t r = (i / kKBlockBytes) % kTileN;
+    const size_t bs = i % kKBlockBytes;
+    const size_t b = (((bs >> 4) ^ (r & 7)) << 4) | (bs & 15);
+    const size_t blk = i / ((size_t)kKBlockBytes * kTileN);   // nt * kblocks + kb
+    n = (blk / kblocks) * kTileN + r;
+    byte = (blk % kblocks) * kKBlockBytes + b;
+}
+
+// 8-bit codes -> tile-major copy, 16 bytes per thread step.
+__global__ void tile_bytes_kernel(const uint4 *rows, size_t ld_u4, size_t N, size_t kblocks, size_t total16,
+                                  uint4 *out) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t n = i / ldh, k = i % ldh;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total16; i += stride) {
+        size_t n, byte;
+        tile_pos(i * 16, kblocks, n, byte);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n < N && byte / 16 < ld_u4) v = rows[n * ld_u4 + byte / 16];
+        out[i] = v;
+    }
+}
+
+// Codebook weights -> fp16 of blockscale * centroid (one rounding), tile-major, for kind::f16.
+__global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
+                                       const float *bscales, size_t bpr, const float *codebook,
+                                       size_t kblocks, size_t total_halves, __half *out) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_halves; i += stride) {
+        size_t n, byte;
+        tile_pos(i * 2, kblocks, n, byte);
+        const size_t k = byte / 2;
         float v = 0.0f;
-        if (k < K) {
+        if (n < N && k < K) {
             const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
             v = __fmul_rn(bscales[n * bpr + k / kCodebookBlock], codebook[nib]);
         }
@@ -645,15 +695,15 @@ __global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, si
 }
 
 // 4-bit codes -> one byte per weight, exactly: e2m1 -> the e4m3 code of the same value,
-// two's-complement nibble -> int8.  [N][ld] bytes, ld a multiple of 16.
+// two's-complement nibble -> int8; tile-major.
 __global__ void expand_nibbles_kernel(int fmt, const uint32_t *rows, size_t ld_words, size_t N, size_t K,
-                                      size_t ld, uint8_t *out) {
-    const size_t total = N * ld;
+                                      size_t kblocks, size_t total, uint8_t *out) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t n = i / ld, k = i % ld;
+        size_t n, k;
+        tile_pos(i, kblocks, n, k);
         uint8_t v = 0;
-        if (k < K) {
+        if (n < N && k < K) {
             const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
             if (fmt == FNN_FMT_I4) {
                 v = (uint8_t)(int8_t)(((int32_t)(nib << 28)) >> 28);
@@ -679,32 +729,38 @@ bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
 }
 
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
-    if (w->tc || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) return FNN_OK;
+    if (w->tc) return FNN_OK;
     FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
-                "first tcgen05 use of a 4-bit weight happened during graph capture; run the plan once "
-                "before capturing it");
-    if (w->fmt == FNN_FMT_I4CB) {
-        const size_t ldb = (w->K * 2 + 15) & ~(size_t)15;
-        FNN_CUDA_CHECK(cudaMalloc(&w->tc, w->N * ldb), FNN_ERR_MEMORY);
-        w->tc_bytes = w->N * ldb;
-        w->tc_ld = ldb;
-        const int nb = (int)std::min<size_t>(div_ceil(w->N * ldb / 2, 256), (size_t)ctx->sm_count * 16);
-        expand_codebook_kernel<<<nb, 256, 0, ctx->stream>>>((const uint32_t *)w->rows, w->ld_u4 * 4, w->N,
-                                                          w->K, w->scales, w->blocks_per_row, w->codebook,
-                                                          ldb, (__half *)w->tc);
-        FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
-        ctx->launches++;
-        return FNN_OK;
+                "first tcgen05 use of a weight happened during graph capture; run the plan once before "
+                "capturing it");
+    const size_t kbytes = (w->fmt == FNN_FMT_I4CB) ? w->K * 2 : w->K;   // operand bytes per row
+    const size_t kblocks = div_ceil(kbytes, (size_t)kKBlockBytes);
+    const size_t total = div_ceil(w->N, (size_t)kTileN) * kblocks * kTileN * kKBlockBytes;
+    void *buf = nullptr;
+    FNN_CUDA_CHECK(cudaMalloc(&buf, total), FNN_ERR_MEMORY);
+    const auto blocks_for = [&](size_t items) {
+        return (int)std::min<size_t>(div_ceil(items, 256), (size_t)ctx->sm_count * 16);
+    };
+    if (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) {
+        tile_bytes_kernel<<<blocks_for(total / 16), 256, 0, ctx->stream>>>(w->rows, w->ld_u4, w->N, kblocks,
+                                                                         total / 16, (uint4 *)buf);
+    } else if (w->fmt == FNN_FMT_I4CB) {
+        expand_codebook_kernel<<<blocks_for(total / 2), 256, 0, ctx->stream>>>(
+            (const uint32_t *)w->rows, w->ld_u4 * 4, w->N, w->K, w->scales, w->blocks_per_row, w->codebook,
+            kblocks, total / 2, (__half *)buf);
+    } else {
+        expand_nibbles_kernel<<<blocks_for(total), 256, 0, ctx->stream>>>(
+            w->fmt, (const uint32_t *)w->rows, w->ld_u4 * 4, w->N, w->K, kblocks, total, (uint8_t *)buf);
     }
-    const size_t ld = (w->K + 15) & ~(size_t)15;
-    FNN_CUDA_CHECK(cudaMalloc(&w->tc, w->N * ld), FNN_ERR_MEMORY);
-    w->tc_bytes = w->N * ld;
-    w->tc_ld = ld;
-    const int blocks = (int)std::min<size_t>(div_ceil(w->N * ld, 256), (size_t)ctx->sm_count * 16);
-    expand_nibbles_kernel<<<blocks, 256, 0, ctx->stream>>>(w->fmt, (const uint32_t *)w->rows, w->ld_u4 * 4,
-                                                          w->N, w->K, ld, (uint8_t *)w->tc);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        cudaFree(buf);
+        return set_error(FNN_ERR_DISPATCH, "tile-major copy: %s", cudaGetErrorString(e));
+    }
     ctx->launches++;
+    w->tc = buf;
+    w->tc_bytes = total;
+    w->tc_kblocks = kblocks;
     return FNN_OK;
 }
 
