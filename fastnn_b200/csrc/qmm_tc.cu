@@ -306,7 +306,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_wait();   // the activation planes, dq and rowsum come from the kernel before this one
     const uint32_t tmem_base = *s_tmem;
     const int total_tiles = p.n_tiles * p.m_tiles;
 
@@ -316,19 +315,43 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
+            auto load_a = [&](int st, int nt, int kb) {
+                if (p.tiled)
+                    bulk_load(s_a + (size_t)st * a_bytes, p.w_tiles + (size_t)(nt * p.kblocks + kb) * a_bytes,
+                              a_bytes, &full[st]);
+                else
+                    tma_load_2d(s_a + (size_t)st * a_bytes, &map_w, &full[st], kb * kKBlockBytes, nt * kTileN);
+            };
+            // The weights do not depend on the kernel before this one on the stream, the activation
+            // planes do: the first ring of weight tiles is requested before griddepcontrol.wait, the
+            // matching activation tiles after it.
+            const int head = (blockIdx.x < total_tiles) ? min(p.stages, p.kblocks) : 0;
+            if (head > 0) {
+                const int nt = blockIdx.x / p.m_tiles, mt = blockIdx.x - nt * p.m_tiles;
+                for (int kb = 0; kb < head; ++kb) {
+                    mbar_expect_tx(&full[kb], (uint32_t)(a_bytes + b_bytes));   // stage kb: all stages start empty
+                    load_a(kb, nt, kb);
+                }
+                pdl_wait();
+                for (int kb = 0; kb < head; ++kb)
+                    tma_load_3d(s_b + (size_t)kb * b_stride, &map_a, &full[kb], kb * kKBlockBytes, mt * p.Mb, 0);
+                s = head;
+                if (s == p.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
+            } else {
+                pdl_wait();
+            }
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-                for (int kb = 0; kb < p.kblocks; ++kb) {
+                for (int kb = (tile == (int)blockIdx.x ? head : 0); kb < p.kblocks; ++kb) {
                     if (!mbar_wait(&empty[s], phase ^ 1, s_abort, p.err_flag, 0x10)) {
                         ok = false;
                         break;
                     }
                     mbar_expect_tx(&full[s], (uint32_t)(a_bytes + b_bytes));
-                    if (p.tiled)
-                        bulk_load(s_a + (size_t)s * a_bytes,
-                                  p.w_tiles + (size_t)(nt * p.kblocks + kb) * a_bytes, a_bytes, &full[s]);
-                    else
-                        tma_load_2d(s_a + (size_t)s * a_bytes, &map_w, &full[s], kb * kKBlockBytes, nt * kTileN);
+                    load_a(s, nt, kb);
                     tma_load_3d(s_b + (size_t)s * b_stride, &map_a, &full[s], kb * kKBlockBytes, mt * p.Mb, 0);
                     if (++s == p.stages) {
                         s = 0;
@@ -384,6 +407,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     } else {
         // ---------------- epilogue (8 warps: a TMEM lane quadrant each, two warps per quadrant
         // taking alternate 16-column chunks) ----------------
+        pdl_wait();   // dq, rowsum and the output buffer belong to kernels before this one
         const int quad = warp & 3;
         const int chunk0 = ((warp - 2) >> 2) * 16;
         int as = 0;
@@ -519,6 +543,11 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
                                          (size_t)(Mpad - M) * Kp, T, ctx->stream),
                        FNN_ERR_DISPATCH);
+    // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
+    // kernels makes every SM reconfigure (and drain) twice per call
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(act_prep_kernel<KIND, T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared),
+                   FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
                    FNN_ERR_DISPATCH);
     ctx->launches++;
@@ -599,6 +628,11 @@ int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size
         FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
                                          (size_t)(Mpad - M) * Kp, T, ctx->stream),
                        FNN_ERR_DISPATCH);
+    // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
+    // kernels makes every SM reconfigure (and drain) twice per call
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(act_prep_kernel<KIND, T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared),
+                   FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
                    FNN_ERR_DISPATCH);
     ctx->launches++;
