@@ -92,7 +92,8 @@ struct fnn_cuda_qweight {
     bool mma_ok = true;         // false when values would leave the fp16 range of that kernel
     // tile-major operand copy for the tcgen05 kernel (built on demand): [row tile of 128][K block of
     // 128 bytes][128 rows][128 bytes], zero padded, so that every TMA box is 16 KB of contiguous memory.
-    // One byte per weight (8-bit codes as stored, I4 -> int8, FP4 -> e4m3) or fp16 (codebook format).
+    // Only for the formats that need an expansion: one byte per weight (I4 -> int8, FP4 -> e4m3) or
+    // fp16 (codebook format); 8-bit codes are read in place from `rows`.
     void *tc = nullptr;
     size_t tc_bytes = 0;
     size_t tc_kblocks = 0;      // K blocks per row tile

@@ -697,19 +697,6 @@ __device__ __forceinline__ void tile_pos(size_t i, size_t kblocks, size_t &n, si
     byte = (blk % kblocks) * kKBlockBytes + b;
 }
 
-// 8-bit codes -> tile-major copy, 16 bytes per thread step.
-__global__ void tile_bytes_kernel(const uint4 *rows, size_t ld_u4, size_t N, size_t kblocks, size_t total16,
-                                  uint4 *out) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total16; i += stride) {
-        size_t n, byte;
-        tile_pos(i * 16, kblocks, n, byte);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (n < N && byte / 16 < ld_u4) v = rows[n * ld_u4 + byte / 16];
-        out[i] = v;
-    }
-}
-
 // Codebook weights -> fp16 of blockscale * centroid (one rounding), tile-major, for kind::f16.
 __global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
                                        const float *bscales, size_t bpr, const float *codebook,
@@ -763,7 +750,10 @@ bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
 }
 
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
-    if (w->tc) return FNN_OK;
+    // 8-bit codes are read in place from the rows (a tile-major copy measured within 4 % of that at
+    // every batch size and would double their footprint); the formats that need a byte or fp16
+    // expansion anyway get it tile-major
+    if (w->tc || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) return FNN_OK;
     FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
                 "first tcgen05 use of a weight happened during graph capture; run the plan once before "
                 "capturing it");
@@ -775,10 +765,7 @@ int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
     const auto blocks_for = [&](size_t items) {
         return (int)std::min<size_t>(div_ceil(items, 256), (size_t)ctx->sm_count * 16);
     };
-    if (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) {
-        tile_bytes_kernel<<<blocks_for(total / 16), 256, 0, ctx->stream>>>(w->rows, w->ld_u4, w->N, kblocks,
-                                                                         total / 16, (uint4 *)buf);
-    } else if (w->fmt == FNN_FMT_I4CB) {
+    if (w->fmt == FNN_FMT_I4CB) {
         expand_codebook_kernel<<<blocks_for(total / 2), 256, 0, ctx->stream>>>(
             (const uint32_t *)w->rows, w->ld_u4 * 4, w->N, w->K, w->scales, w->blocks_per_row, w->codebook,
             kblocks, total / 2, (__half *)buf);
