@@ -433,7 +433,7 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
     int rc = prepare_qmm_mma(ctx, w);
     if (rc != FNN_OK) return rc;
     QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, &g};
-    return launch_qmm_mma(ctx, args);   // 8-bit operand kernel for I8 / I4, fp16 kernel for the rest
+    return launch_qmm_mma(ctx, args);   // 8-bit operand kernel for I8 / I4 / FP4, fp16 kernel for the rest
 }
 
 int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,

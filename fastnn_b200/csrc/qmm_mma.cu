@@ -687,8 +687,9 @@ int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) { return ensure_frag
 int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     int rc = ensure_frag(ctx, const_cast<fnn_cuda_qweight *>(a.w));
     if (rc != FNN_OK) return rc;
-    // up to 8 batch rows the 8-bit operand kernel reads the same fragment layout with far fewer
-    // instructions per weight; the fp16 kernel below serves the codebook format and larger batches
+    // up to four batch rows the 8-bit operand kernel serves I8 / I4 / FP4 from the same fragment layout
+    // with far fewer instructions per weight; the fp16 kernel below serves FP8, the codebook format
+    // and larger batches
     if (qmm_mma8_supported(a.w, a.M)) return launch_qmm_mma8(ctx, a);
     switch (a.w->fmt) {
     case FNN_FMT_I8:

@@ -8,17 +8,15 @@
 //   I4   -> s8 operands holding 16*q: two masks per word of eight codes
 //   FP4  -> s8 operands holding 2*|v| through a byte-permute table, positive and negative codes
 //           in separate operands (two accumulators, subtracted at the end): no sign arithmetic
-//   FP8  -> e4m3 operands as stored (kept for comparison; `mma.sync` on e4m3 is slow on this part)
-// and the f32 activations are rewritten while they are staged, per batch row, as
-//   int8:  a ~= dq * (128*hi + lo)        (15-bit fixed point, exact int32 accumulation)
-//   e4m3:  a ~= dq * (t1 + t2 [+ t3])     (three terms up to 2 batch rows, two beyond)
-// Partial sums of the int formats are integers, so the split-K reduction is exact in any order.
+// (FP8 is not served here: `mma.sync` with e4m3 operands measured slower than the fp16 kernel on this
+// part) and the f32 activations are rewritten while they are staged, per batch row, as
+//   a ~= dq * (128*hi + lo)        (15-bit fixed point, exact int32 accumulation)
+// Partial sums are integers, so the split-K reduction is exact in any order.
 // Epilogue as everywhere:  out = act(dq*acc*scale[n] + zero[n]*sum_k a[m,k] + bias[n])
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
 #include "common.cuh"
 
 #include <algorithm>
-#include <cuda_fp8.h>
 
 namespace fnn {
 
@@ -32,7 +30,6 @@ constexpr int kG8Max = 3;   // groups per block (fewer when a layer has too few 
 template <int FMT>
 struct T8 {
     static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4);
-    static constexpr bool is_int = (FMT != FNN_FMT_F8);
     static constexpr int KBLK = four_bit ? 128 : 64;       // k per k-block (4 lanes x 16 bytes per row)
     static constexpr int MMAS = four_bit ? 4 : 2;          // m16n8k32 MMAs per k-block
     static constexpr int PAD = four_bit ? 16 : 64;         // activation row padding (bank spread)
@@ -60,15 +57,6 @@ __device__ __forceinline__ void mma_s8(int *d, uint32_t a0, uint32_t a1, uint32_
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_e4m3(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // prmt.b32 in its default mode: selector nibble n picks byte n&7 of {a, b}; bit 3 of the nibble
 // replaces the byte by its sign bit replicated eight times.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -119,7 +107,6 @@ struct P8 {
     int M, N, K;
     int KB, ntiles, tiles_per_group;
     int Kc;      // activations staged per pass (multiple of KBLK)
-    int T;       // activation terms (2 for int8; 3 or 2 for e4m3)
     int epilogue;
     int gather_on;
     GatherArgs g;
@@ -130,12 +117,11 @@ __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
 qmm_mma8_kernel(P8 p) {
     using TT = T8<FMT>;
     constexpr int KBLK = TT::KBLK, MMAS = TT::MMAS;
-    constexpr bool INT = TT::is_int;
     constexpr int NT = kG8 * kW8 * 32, NW = kG8 * kW8;
     constexpr int UNITS = kU8 * 2;
     extern __shared__ __align__(16) unsigned char smem[];
     const int RS = p.Kc + TT::PAD;             // bytes per staged activation row
-    const int cols = p.T * p.M;                // (term, batch row) columns in use
+    const int cols = 2 * p.M;                  // (term, batch row) columns in use
     unsigned char *s_ring = smem;                                         // [NW][S][UNITS][32] uint4
     unsigned char *s_act = s_ring + (size_t)NW * kS8 * UNITS * 512;       // [cols][RS]
     float *s_red = reinterpret_cast<float *>(s_act + (((size_t)cols * RS + 15) & ~(size_t)15));
@@ -174,13 +160,11 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
 
-    float accf[CG][4];
     int acci[CG][4], accn[CG][4];   // accn: FP4's negative-weight sums
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            accf[cg][r] = 0.0f;
             acci[cg][r] = 0;
             accn[cg][r] = 0;
         }
@@ -256,7 +240,7 @@ qmm_mma8_kernel(P8 p) {
                         bm = fmaxf(bm, s_part[w * 2]);
                         bs += s_part[w * 2 + 1];
                     }
-                    const float full = INT ? 16256.0f : 448.0f;
+                    const float full = 16256.0f;
                     s_dq[m] = (bm > 0.0f && isfinite(bm)) ? bm / full : 1.0f;
                     s_rs[m] = bs;
                 }
@@ -275,20 +259,11 @@ qmm_mma8_kernel(P8 p) {
             auto put = [&](int k, float a) {
                 const float x = a * inv;
                 const int pos = act_pos8<FMT>(k);
-                if (INT) {
-                    int q = __float2int_rn(x);
-                    q = max(-16256, min(16256, q));
-                    const int hi = (q + 64) >> 7;
-                    s_act[(size_t)m * RS + pos] = (unsigned char)(signed char)hi;
-                    s_act[(size_t)(p.M + m) * RS + pos] = (unsigned char)(signed char)(q - hi * 128);
-                } else {
-                    float r = x;
-                    for (int t = 0; t < p.T; ++t) {
-                        const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-                        s_act[(size_t)(t * p.M + m) * RS + pos] = (unsigned char)code;
-                        r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
-                    }
-                }
+                int q = __float2int_rn(x);
+                q = max(-16256, min(16256, q));
+                const int hi = (q + 64) >> 7;
+                s_act[(size_t)m * RS + pos] = (unsigned char)(signed char)hi;
+                s_act[(size_t)(p.M + m) * RS + pos] = (unsigned char)(signed char)(q - hi * 128);
             };
             if (vec_ok) {
                 const int n4 = kc_len / 4;
@@ -360,16 +335,11 @@ qmm_mma8_kernel(P8 p) {
                         uint4 b = make_uint4(0, 0, 0, 0);
                         if (brow[cg] >= 0)
                             b = *reinterpret_cast<const uint4 *>(s_act + (size_t)brow[cg] * RS + boff + v * 16);
-                        if (INT) {
-                            mma_s8(acci[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                            mma_s8(acci[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
-                            if (FMT == FNN_FMT_F4) {
-                                mma_s8(accn[cg], an[0][0], an[0][1], an[0][2], an[0][3], b.x, b.y);
-                                mma_s8(accn[cg], an[1][0], an[1][1], an[1][2], an[1][3], b.z, b.w);
-                            }
-                        } else {
-                            mma_e4m3(accf[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
-                            mma_e4m3(accf[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                        mma_s8(acci[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
+                        mma_s8(acci[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
+                        if (FMT == FNN_FMT_F4) {
+                            mma_s8(accn[cg], an[0][0], an[0][1], an[0][2], an[0][3], b.x, b.y);
+                            mma_s8(accn[cg], an[1][0], an[1][1], an[1][2], an[1][3], b.z, b.w);
                         }
                     }
                 }
@@ -383,10 +353,9 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         red[(gw * CG + cg) * 128 + r * 32 + lane] =
-                            INT ? (float)(FMT == FNN_FMT_F4 ? acci[cg][r] - accn[cg][r] : acci[cg][r]) : accf[cg][r];
+                            (float)(FMT == FNN_FMT_F4 ? acci[cg][r] - accn[cg][r] : acci[cg][r]);
                         acci[cg][r] = 0;
                         accn[cg][r] = 0;
-                        accf[cg][r] = 0.0f;
                     }
                 group_barrier8(group);
                 for (int e = gtid; e < CG * 128; e += kW8 * 32) {
@@ -415,15 +384,9 @@ qmm_mma8_kernel(P8 p) {
             const int cg = col >> 3, cc = col & 7;
             return my_out[tl * CG * 128 + cg * 128 + ((r16 >> 3) * 2 + (cc & 1)) * 32 + (r16 & 7) * 4 + (cc >> 1)];
         };
-        float acc;
-        if (INT) {
-            acc = at(m) * 128.0f + at(p.M + m);
-            if (FMT == FNN_FMT_I4) acc *= 0.0625f;  // operands carried 16*q
-            if (FMT == FNN_FMT_F4) acc *= 0.5f;     // operands carried 2*|v|
-        } else {
-            acc = at(m) + at(p.M + m);
-            if (p.T == 3) acc += at(2 * p.M + m);
-        }
+        float acc = at(m) * 128.0f + at(p.M + m);
+        if (FMT == FNN_FMT_I4) acc *= 0.0625f;  // operands carried 16*q
+        if (FMT == FNN_FMT_F4) acc *= 0.5f;     // operands carried 2*|v|
         const float *meta = my_meta + (tl * 16 + r16) * 3;
         const float v = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f,
                                       p.bias != nullptr, meta[2], p.epilogue);
@@ -437,7 +400,7 @@ qmm_mma8_kernel(P8 p) {
 }
 
 template <int FMT, int CG, int kG8>
-int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
+int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     using TT = T8<FMT>;
     const fnn_cuda_qweight *w = a.w;
     P8 p{};
@@ -452,11 +415,10 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
     p.K = (int)w->K;
     p.KB = (int)div_ceil(w->K, (size_t)TT::KBLK);
     p.ntiles = (int)div_ceil(w->N, 16);
-    p.T = T;
     p.epilogue = a.epilogue;
     p.gather_on = a.gather != nullptr;
     if (a.gather) p.g = *a.gather;
-    const int cols = T * p.M;
+    const int cols = 2 * p.M;   // int8 pairs
     const int Kpad = p.KB * TT::KBLK;
     const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * 512;
     const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * 2 + 16) * 4 + 64;
@@ -496,16 +458,14 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int T) {
 template <int FMT>
 int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const int M = (int)a.M;
-    // int8 pairs always; e4m3 triples while they fit one 8-column group with the batch, pairs beyond
-    const int T = T8<FMT>::is_int ? 2 : (M <= 2 ? 3 : 2);
-    FNN_REQUIRE(T * M <= 8, FNN_ERR_UNSUPPORTED,
-                "qmatmul: the 8-bit fragment kernel holds one 8-column group (M=%d, %d terms)", M, T);
+    FNN_REQUIRE(2 * M <= 8, FNN_ERR_UNSUPPORTED,
+                "qmatmul: the 8-bit fragment kernel holds one 8-column group of int8 pairs (M=%d)", M);
     // Groups per block: three while that still gives (nearly) every SM a block; layers with fewer row
     // tiles run two or one group per block so that the tiles spread over more SMs.
     const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
-    if ((ntiles + 2) / 3 >= want) return launch8<FMT, 1, 3>(ctx, a, T);
-    if ((ntiles + 1) / 2 >= want) return launch8<FMT, 1, 2>(ctx, a, T);
-    return launch8<FMT, 1, 1>(ctx, a, T);
+    if ((ntiles + 2) / 3 >= want) return launch8<FMT, 1, 3>(ctx, a);
+    if ((ntiles + 1) / 2 >= want) return launch8<FMT, 1, 2>(ctx, a);
+    return launch8<FMT, 1, 1>(ctx, a);
 }
 
 }  // namespace
@@ -513,8 +473,7 @@ int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M) {
     // Measured on B200: s8 operands beat the fp16 fragment kernel up to four batch rows for every
     // format whose values are small integers (I8, I4, and FP4 doubled); `mma.sync` with e4m3 operands
-    // runs at a fraction of the fp16 rate there, so FP8 stays on the fp16 kernel (the e4m3
-    // instantiation remains selectable for comparison).
+    // runs at a fraction of the fp16 rate there, so FP8 stays on the fp16 kernel.
     return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4 || w->fmt == FNN_FMT_F4) && M >= 1 && M <= 4 &&
            w->N < (1u << 27) &&
            w->K < (1u << 27);
@@ -556,8 +515,6 @@ int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         return launch8_fmt<FNN_FMT_I8>(ctx, a);
     case FNN_FMT_I4:
         return launch8_fmt<FNN_FMT_I4>(ctx, a);
-    case FNN_FMT_F8:
-        return launch8_fmt<FNN_FMT_F8>(ctx, a);
     case FNN_FMT_F4:
         return launch8_fmt<FNN_FMT_F4>(ctx, a);
     }
