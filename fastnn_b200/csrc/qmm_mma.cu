@@ -322,62 +322,84 @@ qmm_mma_kernel(MmaParams p) {
             if (CG == 1 && p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
         }
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
-        // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo), two rows at a time ------
-        for (int m0 = 0; m0 < p.M; m0 += 2) {
-            float part[2] = {0.0f, 0.0f};
-            auto put = [&](int mi, int k, float a) {
-                part[mi] += a;
-                if (fabsf(a) > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
-                __half hi = __float2half_rn(a);
-                const int pos = act_pos<FMT>(k);
-                reinterpret_cast<__half *>(s_act + (size_t)(m0 + mi) * RS)[pos] = hi;
-                if (p.split)
-                    reinterpret_cast<__half *>(s_act + (size_t)(p.M + m0 + mi) * RS)[pos] =
-                        __float2half_rn(a - __half2float(hi));
-            };
-            if (vec_ok) {
-                const int n4 = kc_len / 4;
-                for (int b4 = 0; b4 < n4; b4 += 2 * NT) {
-                    float4 v[2][2];
+        // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo) ----------------------------
+        // Work item of a warp = 32 groups of eight consecutive k of one batch row: two 16-byte loads
+        // per lane, one 16-byte store per plane (an 8-group is contiguous in the staged order of every
+        // format), one warp reduction for the row sum.  Two items are in flight per warp.
+        if (has_zero) {
+            for (int m = lane; m < p.M; m += 32) s_rs_part[warp * 64 + m] = 0.0f;
+            __syncwarp();
+        }
+        if (vec_ok) {
+            const int chunks = kc_len / 8, cg32 = (chunks + 31) / 32, witems = p.M * cg32;
+            for (int w0 = warp; w0 < witems; w0 += 2 * NW) {
+                float4 v[2][2];
+                int mm[2], cc[2];
 #pragma unroll
-                    for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            const int i4 = b4 + q * NT + tid;
-                            const int k = k0 + i4 * 4;
-                            v[mi][q] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (m0 + mi < p.M && i4 < n4 && k < p.K)
-                                v[mi][q] = __ldg(reinterpret_cast<const float4 *>(
-                                    p.act + (size_t)(m0 + mi) * p.K + k));
-                        }
-#pragma unroll
-                    for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            const int i4 = b4 + q * NT + tid;
-                            if (m0 + mi < p.M && i4 < n4) {
-                                put(mi, i4 * 4 + 0, v[mi][q].x);
-                                put(mi, i4 * 4 + 1, v[mi][q].y);
-                                put(mi, i4 * 4 + 2, v[mi][q].z);
-                                put(mi, i4 * 4 + 3, v[mi][q].w);
-                            }
-                        }
+                for (int q = 0; q < 2; ++q) {
+                    const int wi = w0 + q * NW;
+                    mm[q] = wi / cg32;
+                    cc[q] = (wi - mm[q] * cg32) * 32 + lane;
+                    v[q][0] = v[q][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (wi < witems && cc[q] < chunks) {
+                        const int k = k0 + cc[q] * 8;
+                        const float *src = p.act + (size_t)mm[q] * p.K + k;
+                        if (k < p.K) v[q][0] = __ldg(reinterpret_cast<const float4 *>(src));
+                        if (k + 4 < p.K) v[q][1] = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+                    }
                 }
-            } else {
-                for (int mi = 0; mi < 2; ++mi) {
-                    if (m0 + mi >= p.M) break;
-                    const float *src = p.act + (size_t)(m0 + mi) * p.K;
-                    for (int k = tid; k < kc_len; k += NT)
-                        put(mi, k, (k0 + k < p.K) ? __ldg(src + k0 + k) : 0.0f);
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int wi = w0 + q * NW;
+                    if (wi >= witems) break;   // warp-uniform
+                    const float e[8] = {v[q][0].x, v[q][0].y, v[q][0].z, v[q][0].w,
+                                        v[q][1].x, v[q][1].y, v[q][1].z, v[q][1].w};
+                    float sum = 0.0f, amax = 0.0f;
+                    __align__(16) __half hi[8];
+                    __align__(16) __half lo[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        sum += e[i];
+                        amax = fmaxf(amax, fabsf(e[i]));
+                        const int pos = FragTraits<FMT>::four_bit ? pos8<FMT>(i) : i;
+                        hi[pos] = __float2half_rn(e[i]);
+                        lo[pos] = __float2half_rn(e[i] - __half2float(hi[pos]));
+                    }
+                    if (amax > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
+                    if (cc[q] < chunks) {
+                        const int base = act_pos<FMT>(cc[q] * 8) * 2;   // bytes; 8-groups stay together
+                        *reinterpret_cast<uint4 *>(s_act + (size_t)mm[q] * RS + base) =
+                            *reinterpret_cast<const uint4 *>(hi);
+                        if (p.split)
+                            *reinterpret_cast<uint4 *>(s_act + (size_t)(p.M + mm[q]) * RS + base) =
+                                *reinterpret_cast<const uint4 *>(lo);
+                    }
+                    if (has_zero) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+                        if (lane == 0) s_rs_part[warp * 64 + mm[q]] += sum;
+                    }
                 }
             }
-            if (has_zero) {
+        } else {
+            for (int m = 0; m < p.M; ++m) {
+                const float *src = p.act + (size_t)m * p.K;
+                float part = 0.0f;
+                for (int k = tid; k < kc_len; k += NT) {
+                    const float a = (k0 + k < p.K) ? __ldg(src + k0 + k) : 0.0f;
+                    part += a;
+                    if (fabsf(a) > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
+                    const __half h = __float2half_rn(a);
+                    const int pos = act_pos<FMT>(k);
+                    reinterpret_cast<__half *>(s_act + (size_t)m * RS)[pos] = h;
+                    if (p.split)
+                        reinterpret_cast<__half *>(s_act + (size_t)(p.M + m) * RS)[pos] =
+                            __float2half_rn(a - __half2float(h));
+                }
+                if (has_zero) {
 #pragma unroll
-                for (int mi = 0; mi < 2; ++mi) {
-                    float v = part[mi];
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-                    if (lane == 0 && m0 + mi < p.M) s_rs_part[warp * 64 + m0 + mi] = v;
+                    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+                    if (lane == 0) s_rs_part[warp * 64 + m] += part;
                 }
             }
         }
