@@ -112,7 +112,9 @@ struct P8 {
     GatherArgs g;
 };
 
-template <int FMT, int CG, int kG8>
+// MULTI: more than one batch row (all rows scanned and staged together); the single-row instantiation
+// keeps the shortest prologue.
+template <int FMT, int CG, int kG8, bool MULTI>
 __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
 qmm_mma8_kernel(P8 p) {
     using TT = T8<FMT>;
@@ -128,7 +130,7 @@ qmm_mma8_kernel(P8 p) {
     float *s_out = s_red + kG8 * 2 * kW8 * CG * 128;                      // [G][tiles_per_group][CG*128]
     float *s_meta = s_out + (size_t)kG8 * p.tiles_per_group * CG * 128;   // [G][tiles_per_group][16][3]
     float *s_part = s_meta + (size_t)kG8 * p.tiles_per_group * 48;        // [NW][2]
-    float *s_dq = s_part + NW * 2;                                        // [8]
+    float *s_dq = s_part + NW * (MULTI ? 8 : 2);   // s_part: [NW][rows (4 when MULTI)][2]                                        // [8]
     float *s_rs = s_dq + 8;                                               // [8]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -208,6 +210,61 @@ qmm_mma8_kernel(P8 p) {
             pdl_wait();
             if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
             // ---- per-row step and sum: max |a| over the whole row first ---------------------
+            if (MULTI) {
+                // all rows in one pass over the activations: one barrier pair instead of one per row
+                float mx[4], sum[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) mx[m] = sum[m] = 0.0f;
+                if (vec_ok) {
+                    for (int i = tid; i < p.K / 4; i += NT) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            if (m < p.M) {
+                                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.act + (size_t)m * p.K) + i);
+                                mx[m] = fmaxf(fmaxf(mx[m], fmaxf(fabsf(v.x), fabsf(v.y))),
+                                              fmaxf(fabsf(v.z), fabsf(v.w)));
+                                sum[m] += (v.x + v.y) + (v.z + v.w);
+                            }
+                        }
+                    }
+                } else {
+                    for (int k = tid; k < p.K; k += NT) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            if (m < p.M) {
+                                const float a = __ldg(p.act + (size_t)m * p.K + k);
+                                mx[m] = fmaxf(mx[m], fabsf(a));
+                                sum[m] += a;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    if (m < p.M) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xFFFFFFFFu, mx[m], o));
+                            sum[m] += __shfl_xor_sync(0xFFFFFFFFu, sum[m], o);
+                        }
+                        if (lane == 0) {
+                            s_part[(warp * 4 + m) * 2] = mx[m];
+                            s_part[(warp * 4 + m) * 2 + 1] = sum[m];
+                        }
+                    }
+                }
+                __syncthreads();
+                if (tid < p.M) {   // one thread per row folds the warps' partials in a fixed order
+                    float bm = 0.0f, bs = 0.0f;
+                    for (int w = 0; w < NW; ++w) {
+                        bm = fmaxf(bm, s_part[(w * 4 + tid) * 2]);
+                        bs += s_part[(w * 4 + tid) * 2 + 1];
+                    }
+                    s_dq[tid] = (bm > 0.0f && isfinite(bm)) ? bm / 16256.0f : 1.0f;
+                    s_rs[tid] = bs;
+                }
+                __syncthreads();
+            } else
             for (int m = 0; m < p.M; ++m) {
                 const float *row = p.act + (size_t)m * p.K;
                 float mx = 0.0f, sum = 0.0f;
@@ -253,6 +310,44 @@ qmm_mma8_kernel(P8 p) {
 
         __syncthreads();  // previous pass fully consumed
         // ---- stage the activation bytes of [k0, k0 + kc_len) --------------------------------
+        if (MULTI && vec_ok && (p.K % 8 == 0)) {
+            // eight activations of every row per thread and step: two 16-byte loads per row in flight,
+            // one 8-byte store per (row, plane)
+            const int n8 = kc_len / 8;
+            for (int i8 = tid; i8 < n8; i8 += NT) {
+                const bool in = k0 + i8 * 8 < p.K;
+                float4 v[4][2];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    v[m][0] = v[m][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (m < p.M && in) {
+                        const float4 *src = reinterpret_cast<const float4 *>(p.act + (size_t)m * p.K + k0 + i8 * 8);
+                        v[m][0] = __ldg(src);
+                        v[m][1] = __ldg(src + 1);
+                    }
+                }
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    if (m < p.M) {
+                        const float inv = 1.0f / s_dq[m];
+                        const float e[8] = {v[m][0].x, v[m][0].y, v[m][0].z, v[m][0].w,
+                                            v[m][1].x, v[m][1].y, v[m][1].z, v[m][1].w};
+                        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            int q = __float2int_rn(e[j] * inv);
+                            q = max(-16256, min(16256, q));
+                            const int h = (q + 64) >> 7;
+                            const int pos = act_pos8<FMT>(j);   // position inside the 8-group
+                            hi[pos >> 2] |= (uint32_t)(h & 0xFF) << ((pos & 3) * 8);
+                            lo[pos >> 2] |= (uint32_t)((q - h * 128) & 0xFF) << ((pos & 3) * 8);
+                        }
+                        *reinterpret_cast<uint2 *>(s_act + (size_t)m * RS + i8 * 8) = make_uint2(hi[0], hi[1]);
+                        *reinterpret_cast<uint2 *>(s_act + (size_t)(p.M + m) * RS + i8 * 8) = make_uint2(lo[0], lo[1]);
+                    }
+                }
+            }
+        } else
         for (int m = 0; m < p.M; ++m) {
             const float *row = p.act + (size_t)m * p.K;
             const float inv = 1.0f / s_dq[m];
@@ -399,7 +494,7 @@ qmm_mma8_kernel(P8 p) {
     if (p.gather_on) gather_finish(p.g, step, p.M, p.N);
 }
 
-template <int FMT, int CG, int kG8>
+template <int FMT, int CG, int kG8, bool MULTI>
 int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     using TT = T8<FMT>;
     const fnn_cuda_qweight *w = a.w;
@@ -421,7 +516,7 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const int cols = 2 * p.M;   // int8 pairs
     const int Kpad = p.KB * TT::KBLK;
     const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * 512;
-    const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * 2 + 16) * 4 + 64;
+    const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * (MULTI ? 8 : 2) + 16) * 4 + 64;
     const size_t per_tile = (size_t)kG8 * (CG * 512 + 192);
     const size_t cap = 226 * 1024;
     // one block per SM whenever the per-group accumulators of ceil(tiles / groups) tiles fit next to
@@ -446,7 +541,7 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     p.Kc = Kc;
     const size_t act_bytes = (((size_t)cols * (Kc + TT::PAD)) + 15) & ~(size_t)15;
     const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
-    auto kern = qmm_mma8_kernel<FMT, CG, kG8>;
+    auto kern = qmm_mma8_kernel<FMT, CG, kG8, MULTI>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(kern, grid, kG8 * kW8 * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
@@ -463,9 +558,12 @@ int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     // Groups per block: three while that still gives (nearly) every SM a block; layers with fewer row
     // tiles run two or one group per block so that the tiles spread over more SMs.
     const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
-    if ((ntiles + 2) / 3 >= want) return launch8<FMT, 1, 3>(ctx, a);
-    if ((ntiles + 1) / 2 >= want) return launch8<FMT, 1, 2>(ctx, a);
-    return launch8<FMT, 1, 1>(ctx, a);
+    const bool multi = M > 1;
+    if ((ntiles + 2) / 3 >= want)
+        return multi ? launch8<FMT, 1, 3, true>(ctx, a) : launch8<FMT, 1, 3, false>(ctx, a);
+    if ((ntiles + 1) / 2 >= want)
+        return multi ? launch8<FMT, 1, 2, true>(ctx, a) : launch8<FMT, 1, 2, false>(ctx, a);
+    return multi ? launch8<FMT, 1, 1, true>(ctx, a) : launch8<FMT, 1, 1, false>(ctx, a);
 }
 
 }  // namespace
