@@ -39,6 +39,9 @@ int ensure_scratch(fnn_cuda_ctx *ctx, size_t bytes) {
 // out[i] = op(a[i % a_len], b[i % b_len]); unary ops read a only.
 __global__ void elementwise_kernel(int op, const float *a, size_t a_len, const float *b,
                                    size_t b_len, float *out, size_t out_len) {
+    // launched as a programmatic dependent: nothing here is independent of the kernel before it
+    pdl_launch_dependents();
+    pdl_wait();
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < out_len; i += stride) {
         float x = a[i % a_len];
@@ -490,9 +493,9 @@ int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_
     const float *a = (const float *)(arena->base + a_offset);
     const float *b = binary ? (const float *)(arena->base + b_offset) : a;
     float *o = (float *)(arena->base + out_offset);
-    elementwise_kernel<<<grid_for(ctx, out_len, 256), 256, 0, ctx->stream>>>(
-        op, a, a_len, b, binary ? b_len : 1, o, out_len);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(elementwise_kernel, grid_for(ctx, out_len, 256), 256, 0, ctx->stream, op, a,
+                              a_len, b, binary ? b_len : (size_t)1, o, out_len),
+                   FNN_ERR_DISPATCH);
     ctx->launches++;
     return FNN_OK;
 }
