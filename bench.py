@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweep]
 
-Workload (config.workload): BASELINE config 2 -- I8 per-channel weights, K=4096, N=11008,
+Workload (config.workload): the I8 sweep configuration -- I8 per-channel weights, K=4096, N=11008,
 f32 activations [M,4096], fused SiLU -- at M=1, the HBM-bound point the metric is quoted on.
 A step is one pass of that layer over one activation batch.  Weights rotate over replicas
 whose total size exceeds the 126 MB L2, so every step streams its weights from HBM.
@@ -12,7 +12,8 @@ whose total size exceeds the 126 MB L2, so every step streams its weights from H
   e2e       the same through the public API with host buffers: pinned H2D of the
             activations and D2H of the result inside every timed step
   roofline  algorithmic bytes per launch / average launch time vs the measured HBM peak
-  sweep     the other (format, M) points of the metric, same method (not the headline)
+  sweep     the other (format, M) points of the metric, same method (not the headline); every point
+            is first checked against the CPU oracle on slices of its output (parity_err)
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank holds an 11008-column
 shard of an [4096, 11008*N] layer, activations are replicated and each step is one kernel per
@@ -43,6 +44,8 @@ SIGMA = 0.02
 L2_BYTES = 126 * 1000 * 1000
 METRIC = "quant_matmul_i8_m1_hbm_gbs"
 UNIT = "GB/s"
+WORKLOAD = ("config2: I8 per-channel weights K=4096 N=11008 per GPU, f32 activations [1,4096], "
+            "fused SiLU")
 
 
 def algorithmic_bytes(fmt_bits: int, n: int, k: int, m: int, n_scales_bytes: int, bias: bool) -> int:
@@ -125,18 +128,21 @@ class ClockSampler:
 class Layer:
     """R device replicas of one quantized weight plus an arena with activation/output slots."""
 
-    def __init__(self, backend, fnn, fmt, w_kn, m, bias=None, min_total_bytes=3 * L2_BYTES):
+    def __init__(self, backend, fnn, fmt, w_kn, m, bias=None, min_total_bytes=3 * L2_BYTES, quantized=None):
         from fastnn_b200 import _lib as L
         self.fnn, self.L, self.backend, self.fmt, self.m = fnn, L, backend, fmt, m
         k, n = w_kn.shape
         self.k, self.n = k, n
-        packed, scales, zeros, cb = fnn.quantize_weight_constant(w_kn, fmt)
+        self.quantized = quantized or fnn.quantize_weight_constant(w_kn, fmt)   # reused across batch sizes
+        packed, scales, zeros, cb = self.quantized
         zp = zeros if fmt in (L.FMT_I8, L.FMT_I4, L.FMT_F4) else np.zeros(0, np.float32)
         meta = fnn.QuantizedWeightMeta(
             bit_width=8 if fmt in (L.FMT_I8, L.FMT_F8) else 4, scales=scales, zero_points=zp,
             shape=[n, k], quant_block_size=32 if fmt == L.FMT_I4CB else 0,
             codebooks=[cb] if fmt == L.FMT_I4CB else [], fmt=fmt)
         self.meta, self.payload = meta, packed.tobytes()
+        self.words, self.scales, self.zp, self.cb = np.frombuffer(self.payload, np.uint32), scales, zp, cb
+        self.bias = bias
         bits = 8 if fmt in (L.FMT_I8, L.FMT_F8) else 4
         wbytes = n * k * bits // 8
         self.replicas = max(2, -(-min_total_bytes // wbytes))
@@ -166,6 +172,50 @@ class Layer:
     def output(self):
         raw = self.backend.read_arena(self.arena, self.out_off, self.m * self.n * 4)
         return np.frombuffer(raw, np.float32).reshape(self.m, self.n)
+
+    def parity_err(self, epi, path=0, max_rows=64, width=64):
+        """One launch on fresh activations, checked against the CPU oracle on three slices of output
+        channels (first, middle, last `width`) and at most `max_rows` batch rows: max |err| / rms."""
+        import oracle as orc   # the checker: never inside a timed region
+        L, n, k, m = self.L, self.n, self.k, self.m
+        x = philox_normal(4242 + m, (m, k), 1.0)
+        self.set_activations(x)
+        self.launch(0, epi, path)
+        got = self.output()
+        width = min(width, n)
+        mid = (n // 2) // 16 * 16 + (8 if n >= 4 * width else 0)
+        rows = np.unique(np.concatenate([np.arange(0, width), np.arange(mid, min(mid + width, n)),
+                                         np.arange(n - width, n)]))
+        ms = np.arange(m) if m <= max_rows else np.arange(0, m, m // max_rows)[:max_rows]
+        wpr = -(-k // (4 if self.fmt in (L.FMT_I8, L.FMT_F8) else 8))
+        sub_words = np.concatenate([self.words[: n * wpr].reshape(n, wpr)[rows].reshape(-1),
+                                    np.zeros(16, np.uint32)])
+        if self.fmt == L.FMT_I4CB:
+            bpr = -(-k // 32)
+            sub = orc.QWeight(self.fmt, len(rows), k, sub_words,
+                              self.scales.reshape(n, bpr)[rows].reshape(-1).copy(), np.zeros(0, np.float32),
+                              self.cb, 32)
+        else:
+            sub = orc.QWeight(self.fmt, len(rows), k, sub_words, self.scales[rows].copy(),
+                              self.zp[rows].copy() if self.zp.size else np.zeros(0, np.float32))
+        want = orc.qmatmul(sub, x[ms], self.bias[rows] if self.has_bias else None, epi).astype(np.float64)
+        err = np.max(np.abs(got[np.ix_(ms, rows)] - want)) / max(np.sqrt(np.mean(want ** 2)), 1e-30)
+        return float(err)
+
+    def time_isolated(self, epi, path=0, reps=20):
+        """Median CUDA-event time of single launches, each alone on the stream (synchronize and an L2
+        flush before it: no neighbouring kernel to overlap with, weights cold)."""
+        b, lib = self.backend, self.backend.lib
+        times, ms = [], ctypes.c_float()
+        for i in range(reps):
+            check(lib.fnn_cuda_flush_l2(b.ctx), self.fnn)
+            b.synchronize()
+            check(lib.fnn_cuda_timer_start(b.ctx, 1), self.fnn)
+            self.launch(i, epi, path)
+            check(lib.fnn_cuda_timer_stop(b.ctx, 1), self.fnn)
+            check(lib.fnn_cuda_timer_elapsed_ms(b.ctx, 1, ctypes.byref(ms)), self.fnn)
+            times.append(float(ms.value))
+        return float(np.median(times))
 
     def time_steps(self, steps, warmup, epi, path=0, min_seconds=0.0):
         """CUDA-event time of `steps` launches replayed from one captured graph."""
@@ -250,17 +300,21 @@ def cpu_baseline(w_kn, budget_s=12.0, max_iters=50):
 
 def sweep_points(L):
     return [  # label, fmt, K, N, Ms, sigma, epilogue, bias
-        ("c2_i8", L.FMT_I8, 4096, 11008, (1, 16, 128, 512), 0.02, L.EPI_SILU, False),
+        ("c2_i8", L.FMT_I8, 4096, 11008, (1, 4, 16, 128, 512), 0.02, L.EPI_SILU, False),
         ("c1_i4", L.FMT_I4, 4096, 4096, (1, 8), 0.02, L.EPI_NONE, True),
         ("c3_i4", L.FMT_I4, 8192, 28672, (1,), 0.015, L.EPI_NONE, False),
         ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
         ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
         ("c4_i4cb_up", L.FMT_I4CB, 2048, 8192, (1, 64), 0.02, L.EPI_GELU, True),
+        ("c4_i4cb_down", L.FMT_I4CB, 8192, 2048, (64,), 0.02, L.EPI_NONE, True),
+        ("i4cb_8192x8192", L.FMT_I4CB, 8192, 8192, (1,), 0.02, L.EPI_NONE, False),
         ("c5_i4_gateup", L.FMT_I4, 4096, 28672, (64,), 0.02, L.EPI_NONE, False),
+        ("c5_i4_down", L.FMT_I4, 14336, 4096, (64,), 0.02, L.EPI_NONE, False),
+        ("c5_i4_qkv", L.FMT_I4, 4096, 6144, (64,), 0.02, L.EPI_NONE, False),
     ]
 
 
-def run_sweep(fnn, backend, peaks, budget_s=240.0, only=None, only_m=None, steps_override=None,
+def run_sweep(fnn, backend, peaks, budget_s=420.0, only=None, only_m=None, steps_override=None,
               path=0):
     from fastnn_b200 import _lib as L
     out, t_start = [], time.time()
@@ -279,19 +333,25 @@ def run_sweep(fnn, backend, peaks, budget_s=240.0, only=None, only_m=None, steps
             cache[key] = philox_normal(7, (k, n), sigma)
         w = cache[key]
         bias = philox_normal(8, (n,), 0.01) if has_bias else None
+        quantized = None
         for m in ms:
-            layer = Layer(backend, fnn, fmt, w, m, bias)
+            layer = Layer(backend, fnn, fmt, w, m, bias, quantized=quantized)
+            quantized = layer.quantized
             try:
+                err = layer.parity_err(epi, path)       # checked before it is timed
                 layer.set_activations(philox_normal(9, (m, k), 1.0))
                 est = max(layer.alg_bytes / 3e12, layer.flops / 2e13)
                 steps = steps_override or int(min(200, max(5, 0.05 / est)))
                 ms_total = layer.time_steps(steps, 3, epi, path)
                 t = ms_total / steps * 1e-3
+                iso = layer.time_isolated(epi, path, reps=10 if est < 1e-4 else 3)
                 gbs, tfs = layer.alg_bytes / t / 1e9, layer.flops / t / 1e12
                 out.append({"point": label, "m": m, "k": k, "n": n, "path": backend.last_path(),
-                            "us": round(t * 1e6, 2), "gbs": round(gbs, 1), "tflops": round(tfs, 2),
+                            "us": round(t * 1e6, 2), "isolated_us": round(iso * 1e3, 2),
+                            "gbs": round(gbs, 1), "tflops": round(tfs, 2),
                             "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
-                            "tensor_frac_bf16": round(tfs / peaks["bf16_tflops"], 3)})
+                            "tensor_frac_bf16": round(tfs / peaks["bf16_tflops"], 3),
+                            "parity_err": float(f"{err:.3g}")})
             finally:
                 layer.close()
     return out
@@ -310,8 +370,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    stream = torch.cuda.current_stream().cuda_stream
-    backend = fnn.CudaBackend(local, stream=stream)
+    backend = fnn.CudaBackend(local)   # its own non-blocking stream: CUDA graphs are captured on it
     peaks = load_peaks()
     if args.only:  # one sweep point only (profiling aid): prints that point and exits
         pts = run_sweep(fnn, backend, peaks, only=args.only, only_m=args.only_m,
@@ -323,6 +382,7 @@ def run_ours(args):
     # every rank owns an 11008-column shard (seeded by rank) of the [4096, 11008*world] layer
     w_kn = philox_normal(1000 + rank, (K_DIM, N_DIM), SIGMA)
     layer = Layer(backend, fnn, L.FMT_I8, w_kn, M_HEAD)
+    head_err = layer.parity_err(L.EPI_SILU)      # the timed kernel's output against the CPU oracle
     layer.set_activations(philox_normal(1, (M_HEAD, K_DIM), 1.0))
 
     sampler = ClockSampler(local)
@@ -357,10 +417,9 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(per_step_s * 1e3, 6),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": "config2: I8 per-channel weights K=4096 N=11008 per GPU, "
-                                   "f32 activations [1,4096], fused SiLU",
+            "config": {"workload": WORKLOAD,
                        "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM, "format": "i8",
-                       "kernel_path": path,
+                       "kernel_path": path, "parity_err": float(f"{head_err:.3g}"),
                        "l2": f"weights rotate over {layer.replicas} replicas "
                              f"({layer.replicas * K_DIM * N_DIM // 1000000} MB > 126 MB L2)",
                        "parallelism": "single GPU" if world == 1 else
@@ -369,10 +428,18 @@ def run_ours(args):
                        "algorithmic_bytes_per_step_per_gpu": layer.alg_bytes},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": peaks["source"]},
+                         "traffic": NCU_TRAFFIC.get(("i8", K_DIM, N_DIM, M_HEAD), {}).get("bytes"),
+                         "traffic_source": NCU_TRAFFIC.get(("i8", K_DIM, N_DIM, M_HEAD), {}).get("source"),
+                         "peak_source": peaks["source"]},
             "clocks": clocks, "gpu_launches": launches,
         }
     if world == 1:
+        iso_ms = layer.time_isolated(L.EPI_SILU)
+        line["isolated_us"] = round(iso_ms * 1e3, 2)
+        line["roofline"]["isolated_frac"] = round(layer.alg_bytes / (iso_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        line["roofline"]["note"] = ("achieved/frac: back-to-back replay of one CUDA graph (the next launch's "
+                                    "weight prefetch overlaps this one's tail); isolated_frac: one launch alone "
+                                    "on the stream after an L2 flush")
         e2e_s, e2e_launches, h2d, d2h, _ = run_e2e(fnn, backend, w_kn, min(args.steps, 2000),
                                                    args.warmup)
         line["e2e"] = {"value": round(layer.alg_bytes / e2e_s / 1e9, 1), "unit": UNIT,
@@ -406,10 +473,13 @@ def run_ours(args):
     backend.close()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel
-# (qmm_mma8_kernel, I8, K=4096, N=11008, M=1), from the ncu capture summarised in
-# profiles/qmm_mma8_i8_m1_config2.md: 45.2326 MB read + 1.3 KB written.
-NCU_TRAFFIC_BYTES = 45233920
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, keyed by (format, K, N, M), from ncu
+# captures of `python bench.py --only <point> --only-m <M>`; `source` names the kernel and the date
+# of the capture.  A point without an entry reports null.
+NCU_TRAFFIC = {
+    ("i8", 4096, 11008, 1): {"bytes": 45233920,
+                             "source": "qmm_mma8_kernel, ncu --set full, 2026-11-25: 45.2326 MB read + 1.3 KB written"},
+}
 
 
 def time_sharded(torch, dist, backend, layer, args, world, L):
@@ -584,10 +654,11 @@ def run_reference(args):
     x = philox_normal(1, (M_HEAD, K_DIM), 1.0)
     sbytes = q.scales.nbytes + q.zeros.nbytes
     alg = algorithmic_bytes(8, N_DIM, K_DIM, M_HEAD, sbytes, False)
-    for _ in range(min(args.warmup, 3)):
+    warm = min(args.warmup, 50)
+    for _ in range(warm):
         orc.qmatmul(q, x, None, orc.EPI_SILU)
     steps = args.steps
-    t_budget, t0, done = 120.0, time.perf_counter(), 0
+    t_budget, t0, done = 170.0, time.perf_counter(), 0
     while done < steps and time.perf_counter() - t0 < t_budget:
         orc.qmatmul(q, x, None, orc.EPI_SILU)
         done += 1
@@ -597,12 +668,10 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
-        "steps": done, "warmup": min(args.warmup, 3), "ms_per_step": round(dt * 1e3, 4),
+        "steps": done, "warmup": warm, "ms_per_step": round(dt * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "config2: I8 per-channel weights K=4096 N=11008, f32 activations "
-                               "[1,4096], fused SiLU", "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM,
-                   "format": "i8"},
+        "config": {"workload": WORKLOAD, "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM, "format": "i8"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
                          "sample": f"{done} full M=1 layer calls; the reference threads only when "
                                    f"M >= physical cores ({info['physical_cores']}); simd_level="

@@ -26,6 +26,7 @@ _vp, _sz, _int, _i64, _f = _c.c_void_p, _c.c_size_t, _c.c_int, _c.c_int64, _c.c_
 SIGNATURES = {
     "fnn_cuda_ctx_create": (_int, [_int, _c.POINTER(_vp)]),
     "fnn_cuda_ctx_create_on_stream": (_int, [_int, _vp, _c.POINTER(_vp)]),
+    "fnn_cuda_ctx_stream": (_vp, [_vp]),
     "fnn_cuda_ctx_destroy": (_int, [_vp]),
     "fnn_cuda_sync": (_int, [_vp]),
     "fnn_cuda_last_error": (_c.c_char_p, []),

@@ -23,7 +23,7 @@ import numpy as np
 
 from . import _lib as L
 
-DimExpr = Union[int, str]  # Known(u64) | Symbol(name)
+DimExpr = Union[int, str, tuple]  # Known(u64) | Symbol(name) | product of DimExprs
 SYMBOL_DIM_MAX = 8192  # src/ir/node.rs:154-160
 
 
@@ -115,6 +115,11 @@ class ShapeEnv(dict):
     """Runtime values of symbolic dimension names (src/ir/node.rs:347-495)."""
 
     def resolve(self, d: DimExpr) -> int:
+        if isinstance(d, tuple):   # a product, e.g. the batch rows of a [d1, 8, K] activation
+            out = 1
+            for f in d:
+                out *= self.resolve(f)
+            return out
         if isinstance(d, str):
             if d not in self:
                 raise BackendError("Dispatch", f"unresolved symbolic dimension '{d}'")

@@ -575,17 +575,21 @@ def lower_to_plan(graph: ComputeGraph, memory_plan: MemoryPlan) -> ExecutablePla
                     "UnsupportedOp",
                     "f32 MatMul is outside the CUDA backend's path (weights must be quantized "
                     "constants; runtime inputs and parameters stay f32 in the reference too)")
+            # M is the product of the activation's leading dimensions; with a symbolic one among
+            # them it is carried as the tuple of all of them and multiplied out once the ShapeEnv
+            # is known (ShapeEnv.resolve), like the param_dims of the elementwise and norm arms
             a_shape = a.output_type.shape
-            m_dim: DimExpr = 1
+            lead = list(a_shape[:-1])
             m_static = 1
-            for d in a_shape[:-1]:
-                if isinstance(d, str):
-                    m_dim = d if m_dim == 1 else m_dim
-                    m_static *= SYMBOL_DIM_MAX
-                else:
-                    m_static *= int(d)
-                    if not isinstance(m_dim, str):
-                        m_dim = m_static
+            for d in lead:
+                m_static *= SYMBOL_DIM_MAX if isinstance(d, str) else int(d)
+            symbolic = [d for d in lead if isinstance(d, str)]
+            if not symbolic:
+                m_dim: DimExpr = m_static
+            elif len(lead) == 1:
+                m_dim = lead[0]
+            else:
+                m_dim = tuple(lead)
             k, nn = int(wt.shape[0]), int(wt.shape[1])
             fused = n.attrs.get("fused_op")
             inputs = [_slice(memory_plan, i) for i in n.inputs]

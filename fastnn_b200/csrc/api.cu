@@ -24,14 +24,14 @@ int ensure_scratch(fnn_cuda_ctx *ctx, size_t bytes) {
                 "scratch buffer must grow (%zu -> %zu bytes) during graph capture; run the "
                 "plan once before capturing it",
                 ctx->scratch_bytes, bytes);
-    if (ctx->scratch) {
-        FNN_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), FNN_ERR_MEMORY);
-        FNN_CUDA_CHECK(cudaFree(ctx->scratch), FNN_ERR_MEMORY);
-        ctx->scratch = nullptr;
-        ctx->scratch_bytes = 0;
-    }
+    // A captured graph may hold the old buffer's address (kernel arguments, memset nodes, tensor
+    // maps), so an outgrown buffer is never freed while the context lives: it is retired and
+    // released by fnn_cuda_ctx_destroy.
     size_t want = bytes + (bytes >> 2);
-    FNN_CUDA_CHECK(cudaMalloc(&ctx->scratch, want), FNN_ERR_MEMORY);
+    void *grown = nullptr;
+    FNN_CUDA_CHECK(cudaMalloc(&grown, want), FNN_ERR_MEMORY);
+    if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch);
+    ctx->scratch = grown;
     ctx->scratch_bytes = want;
     return FNN_OK;
 }
@@ -104,7 +104,7 @@ extern "C" {
 
 const char *fnn_cuda_last_error(void) { return g_err; }
 
-int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) {
+static int ctx_create(int device, bool use_given_stream, void *stream, fnn_cuda_ctx **out) {
     clear_error();
     FNN_REQUIRE(out != nullptr, FNN_ERR_DISPATCH, "ctx_create: out is null");
     *out = nullptr;
@@ -124,8 +124,8 @@ int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) 
     ctx->cc_major = prop.major;
     ctx->cc_minor = prop.minor;
     ctx->total_mem = prop.totalGlobalMem;
-    if (stream) {
-        ctx->stream = (cudaStream_t)stream;
+    if (use_given_stream) {
+        ctx->stream = (cudaStream_t)stream;   // a null handle is the legacy default stream
         ctx->owns_stream = false;
     } else {
         cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
@@ -146,9 +146,13 @@ int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) 
     return FNN_OK;
 }
 
-int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out) {
-    return fnn_cuda_ctx_create_on_stream(device, nullptr, out);
+int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out) { return ctx_create(device, false, nullptr, out); }
+
+int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) {
+    return ctx_create(device, true, stream, out);
 }
+
+void *fnn_cuda_ctx_stream(fnn_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
 int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx) {
     if (!ctx) return FNN_OK;
@@ -160,6 +164,7 @@ int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx) {
     }
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (void *p : ctx->retired_scratch) cudaFree(p);
     if (ctx->err_flag) cudaFree(ctx->err_flag);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -424,7 +429,7 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
                 n_stride, w->N);
     FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
                 "qmatmul_gather: unknown epilogue %d", epilogue);
-    FNN_REQUIRE(M >= 1 && M <= (size_t)kGatherRows && w->mma_ok && qmm_mma_supported(w, M), FNN_ERR_UNSUPPORTED,
+    FNN_REQUIRE(M >= 1 && M <= (size_t)kGatherRows && qmm_mma_supported(w, M), FNN_ERR_UNSUPPORTED,
                 "qmatmul_gather: the fused gather serves 1..%d batch rows on the fragment kernels "
                 "(fmt=%d, M=%zu, K=%zu); gather other cases with a collective", kGatherRows, w->fmt, M, w->K);
     GatherArgs g{};

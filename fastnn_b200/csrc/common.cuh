@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <string>
+#include <vector>
 
 #include "../../include/fastnn_cuda.h"
 
@@ -62,6 +63,7 @@ struct fnn_cuda_ctx {
     // scratch for the tensor-core paths (activation conversion, split-K partials)
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    std::vector<void *> retired_scratch;   // outgrown scratch buffers (captured graphs may still name them)
     int *err_flag = nullptr;  // device flag written by bounded waits that gave up
 };
 
@@ -89,7 +91,8 @@ struct fnn_cuda_qweight {
     uint4 *frag = nullptr;
     size_t frag_bytes = 0;
     float *frag_bs = nullptr;   // I4CB block scales in fragment order
-    bool mma_ok = true;         // false when values would leave the fp16 range of that kernel
+    bool fp16_ok = true;         // codebook format: false when block scales or centroids would leave the fp16 range
+                                // of the tcgen05 kernel's dequantized operand
     // tile-major operand copy for the tcgen05 kernel (built on demand): [row tile of 128][K block of
     // 128 bytes][128 rows][128 bytes], zero padded, so that every TMA box is 16 KB of contiguous memory.
     // Only for the formats that need an expansion: one byte per weight (I4 -> int8, FP4 -> e4m3) or
@@ -357,7 +360,7 @@ int launch_gather_wait(fnn_cuda_ctx *ctx, const unsigned long long *my_words, co
                        int world, int n_stride, float *out);
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 // shapes automatic dispatch sends to the skinny tensor-core kernel
-static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->mma_ok && w->K >= 512 && w->N >= 64; }
+static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->K >= 512 && w->N >= 64; }
 bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M);
 int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &args);
 void free_qweight_aux(fnn_cuda_qweight *w);

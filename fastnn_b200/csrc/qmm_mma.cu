@@ -1,12 +1,14 @@
-// Skinny-M tensor-core kernel for the quantized MatMul (1 <= M <= 64 per launch).
+// Skinny-M tensor-core kernel for the quantized MatMul on fp16 operands (1 <= M <= 64 per launch).
 //
 // The op is bound by the HBM scan of the packed weights, so the kernel is built around that
 // scan: weights live in a fragment-major layout where every warp-wide 128-bit load reads 512
 // contiguous bytes and each lane receives exactly the codes of its own `mma.sync` A fragment
 // (16 weight rows x 16 k).  Codes are expanded to exact fp16 in registers (byte/nibble
 // permutes and half2 arithmetic, ~1 ALU op per weight), activations are staged once per block
-// in shared memory as fp16 (two-term hi/lo split for M <= 16, which keeps f32-grade accuracy),
-// products accumulate in f32 in the tensor cores, K is split across the warps of a block and
+// in shared memory as fp16 -- each row scaled by a power of two so that its largest element sits
+// just below 2^15 (any f32 magnitude is representable, small rows keep their low bits), and split
+// into two terms hi + lo up to 32 batch rows, which keeps f32-grade accuracy -- products
+// accumulate in f32 in the tensor cores, K is split across the warps of a block and
 // reduced through shared memory in a fixed order, and the affine step, bias and activation
 // are applied in the epilogue:
 //   out[m,n] = act(acc[m,n] * scale[n] + zero[n] * sum_k a[m,k] + bias[n])
@@ -16,9 +18,7 @@
 // 128 k for 4-bit), half h (rows g / g+8) and lane l = g*4 + c, the 16-byte unit
 //   frag[((rt*KB + kb)*2 + h)*32 + l]  ==  bytes [ (kb*4 + c)*16, +16 ) of reference row rt*16 + h*8 + g.
 // It is a permutation of the reference's 16-byte units: no bit inside a unit changes.
-#include "common.cuh"
-
-#include <algorithm>
+#include "frag_common.cuh"
 
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
@@ -27,13 +27,19 @@ namespace fnn {
 
 namespace {
 
-constexpr int kW = 8;             // warps per block
-constexpr int kThreadsMma = kW * 32;
-constexpr int kU = 2;             // k-blocks per prefetch chunk
+using frag::cp_async16;
+using frag::cp_async4;
+using frag::cp_async_commit;
+using frag::cp_async_wait;
+using frag::group_barrier;
+
+constexpr int kW = frag::kWarpsPerGroup;   // warps per group
+constexpr int kU = frag::kChunkBlocks;     // k-blocks per prefetch chunk
+constexpr int kMaxRows = 64;               // batch rows per launch
 
 template <int FMT>
 struct FragTraits {
-    static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4 || FMT == FNN_FMT_I4CB);
+    static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4);
     static constexpr int KBLK = four_bit ? 128 : 64;  // k per k-block (4 lanes x 16 bytes per row)
     static constexpr int VEC = four_bit ? 4 : 2;      // B vectors (2 MMAs each) per k-block
     static constexpr int PAD_BYTES = four_bit ? 64 : 16;  // row padding of the activation tile
@@ -80,7 +86,7 @@ struct MmaDec;
 
 template <>
 struct MmaDec<FNN_FMT_I8> {
-    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *, uint32_t) {
+    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h) {
         uint32_t x = w ^ 0x80808080u;  // q + 128
         h[0] = h2_sub(__byte_perm(x, 0x64646464u, 0x4140), 0x64806480u);  // (1024+u) - 1152
         h[1] = h2_sub(__byte_perm(x, 0x64646464u, 0x4342), 0x64806480u);
@@ -89,7 +95,7 @@ struct MmaDec<FNN_FMT_I8> {
 
 template <>
 struct MmaDec<FNN_FMT_I4> {
-    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *, uint32_t) {
+    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h) {
         uint32_t x = w ^ 0x88888888u;  // q + 8 per nibble
         uint32_t y = x >> 8;
         h[0] = h2_sub((x & 0x000F000Fu) | 0x64006400u, 0x64086408u);               // (e0,e4)
@@ -101,7 +107,7 @@ struct MmaDec<FNN_FMT_I4> {
 
 template <>
 struct MmaDec<FNN_FMT_F8> {
-    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *, uint32_t) {
+    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h) {
         __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xFFFFu), __NV_E4M3);
         __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
         h[0] = *reinterpret_cast<uint32_t *>(&lo);
@@ -111,7 +117,7 @@ struct MmaDec<FNN_FMT_F8> {
 
 template <>
 struct MmaDec<FNN_FMT_F4> {
-    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *, uint32_t) {
+    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h) {
         // e2m1 is a tiny float: its (e1 e0 m) bits dropped into fp16 bits [11:9] read as
         // 2^(e-15)*(1+m/2) (or the subnormal m*2^-15), so one multiply by 2^14 rebiases it exactly.
         // Nibbles i and i+4 sit at the same offset of the two halves and move with one shift.
@@ -120,17 +126,6 @@ struct MmaDec<FNN_FMT_F4> {
         h[1] = h2_mul(((w << 5) & kMag) | ((w << 8) & kSign), kTwo14);   // (e1,e5)
         h[2] = h2_mul(((w << 1) & kMag) | ((w << 4) & kSign), kTwo14);   // (e2,e6)
         h[3] = h2_mul(((w >> 3) & kMag) | (w & kSign), kTwo14);          // (e3,e7)
-    }
-};
-
-template <>
-struct MmaDec<FNN_FMT_I4CB> {
-    // lut: per-lane copy of the 256-entry table byte -> half2(cb[lo nibble], cb[hi nibble]);
-    // bs2: half2 of the lane's block scale (a 16-byte unit is exactly one 32-element block).
-    __device__ __forceinline__ static void run(uint32_t w, uint32_t *h, const uint32_t *lut,
-                                               uint32_t bs2) {
-#pragma unroll
-        for (int b = 0; b < 4; ++b) h[b] = h2_mul(lut[((w >> (8 * b)) & 0xFFu) * 32], bs2);
     }
 };
 
@@ -145,14 +140,11 @@ __device__ __forceinline__ void mma_16816(float *d, uint32_t a0, uint32_t a1, ui
 
 struct MmaParams {
     const uint4 *frag;
-    const float *frag_bs;  // I4CB block scales in fragment order
     const float *scales;
     const float *zeros;
-    const float *codebook;
     const float *act;
     float *out;
     const float *bias;
-    int *err_flag;
     int M, N, K;
     int KB;          // k-blocks per row (padded)
     int ntiles;      // row tiles of 16
@@ -165,34 +157,10 @@ struct MmaParams {
 };
 
 // Warp groups per block for a given number of 8-column groups (register budget).
-// (the codebook format also keeps a 32 KB lookup table in shared memory, so it runs two groups)
-__host__ __device__ constexpr int groups_for(int fmt, int cg) {
-    return cg == 1 ? (fmt == FNN_FMT_I4CB ? 2 : 3) : (cg <= 4 ? 2 : 1);
-}
+__host__ __device__ constexpr int groups_for(int cg) { return cg == 1 ? 3 : (cg <= 4 ? 2 : 1); }
 
 // Stages of each lane's private cp.async ring (weights in flight = STAGES - 1 chunks per lane).
 __host__ __device__ constexpr int stages_for(int cg) { return cg == 4 ? 2 : 3; }
-
-__device__ __forceinline__ void group_barrier(int group) {
-    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kW * 32) : "memory");
-}
-
-// 16-byte global -> shared copy that bypasses registers; src_bytes == 0 writes zeros.
-__device__ __forceinline__ void cp_async16(void *dst, const void *src, int src_bytes) {
-    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async4(void *dst, const void *src, int src_bytes) {
-    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // One block per SM.  Its G groups of 8 warps share the staged activations; each group streams
 // its own row tiles, splitting K across its warps.
@@ -210,15 +178,16 @@ qmm_mma_kernel(MmaParams p) {
     const int RS = 2 * p.Kc + T::PAD_BYTES;  // bytes per staged activation row
     const int act_rows = p.split ? 2 * p.M : p.M;  // only real batch rows are staged
     unsigned char *s_ring = smem;                                         // [NW][S][UNITS][32] uint4
-    float *s_ring_bs = reinterpret_cast<float *>(s_ring + (size_t)NW * S * UNITS * 512);  // I4CB only
-    unsigned char *s_act = reinterpret_cast<unsigned char *>(
-        s_ring_bs + (FMT == FNN_FMT_I4CB ? (size_t)NW * S * UNITS * 32 : 0));
+    unsigned char *s_act = s_ring + (size_t)NW * S * UNITS * 512;
     float *s_red = reinterpret_cast<float *>(s_act + (size_t)act_rows * RS);  // [G][2][kW][CG*128]
     float *s_out = s_red + G * 2 * kW * CG * 128;                         // [G][tiles_per_group][CG*128]
-    float *s_rs_part = s_out + (size_t)G * p.tiles_per_group * CG * 128;  // [NW][64]
-    float *s_rs = s_rs_part + NW * 64;                                    // [64]
-    float *s_meta = s_rs + 64;                                            // [G][tiles_per_group][16][3]
-    uint32_t *s_lut = reinterpret_cast<uint32_t *>(s_meta + (size_t)G * p.tiles_per_group * 48);  // I4CB: [256][32]
+    const int Mr = (p.M + 3) & ~3;
+    float *s_part = s_out + (size_t)G * p.tiles_per_group * CG * 128;     // [NW][Mr][2]
+    float *s_rs = s_part + NW * Mr * 2;                                   // [Mr] row sums
+    float *s_mx = s_rs + Mr;                                              // [Mr] row maxima
+    float *s_up = s_mx + Mr;                                              // [Mr] power-of-two row factor
+    float *s_dq = s_up + Mr;                                              // [Mr] its inverse
+    float *s_meta = s_dq + Mr;                                            // [G][tiles_per_group][16][3]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = warp / kW, gw = warp % kW, gtid = tid - group * kW * 32;
@@ -236,26 +205,17 @@ qmm_mma_kernel(MmaParams p) {
     float *my_red = s_red + (size_t)group * 2 * kW * CG * 128;
 
     unsigned char *my_ring = s_ring + (size_t)warp * S * UNITS * 512 + lane * 16;
-    float *my_ring_bs = s_ring_bs + (size_t)warp * S * UNITS * 32 + lane;
 
     // scale / zero / bias of the group's rows: fetched now, used by the epilogue
     float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
     for (int i = gtid; i < tiles_here * 16; i += kW * 32) {
         const int n = (gg + (i >> 4) * GG) * 16 + (i & 15);
         const bool in = n < p.N;
-        my_meta[i * 3 + 0] = (in && FMT != FNN_FMT_I4CB) ? __ldg(p.scales + n) : 1.0f;
+        my_meta[i * 3 + 0] = in ? __ldg(p.scales + n) : 1.0f;
         my_meta[i * 3 + 1] = (in && has_zero) ? __ldg(p.zeros + n) : 0.0f;
         my_meta[i * 3 + 2] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
     }
     for (int i = tid; i < G * p.tiles_per_group * CG * 128; i += NT) s_out[i] = 0.0f;
-    if (tid < 64) s_rs[tid] = 0.0f;
-    if (FMT == FNN_FMT_I4CB) {
-        for (int i = tid; i < 256 * 32; i += NT) {
-            int b = i >> 5;
-            __half2 v = __floats2half2_rn(p.codebook[b & 15], p.codebook[b >> 4]);
-            s_lut[i] = *reinterpret_cast<uint32_t *>(&v);
-        }
-    }
     // staged row holding batch column (cg*8 + g), or -1 when that column carries no batch row
     int brow[CG];
 #pragma unroll
@@ -296,13 +256,9 @@ qmm_mma_kernel(MmaParams p) {
                 const bool ok = valid && (kb < KBc);
                 const size_t idx = ok ? tile_unit + (size_t)kb * 64 : 0;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < 2; ++h)
                     cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + h) * 512, p.frag + idx + h * 32,
                                ok ? 16 : 0);
-                    if (FMT == FNN_FMT_I4CB)
-                        cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + h) * 32, p.frag_bs + idx + h * 32,
-                                  ok ? 4 : 0);
-                }
             }
             cp_async_commit();
             if (++i_j == cpw) {
@@ -320,16 +276,23 @@ qmm_mma_kernel(MmaParams p) {
             // kernel before this one on the stream; the activations and the gather counters are not
             pdl_wait();
             if (CG == 1 && p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
+            // per-row maximum and sum; the row is staged as a * 2^e with the largest element in
+            // [2^14, 2^15): exact, inside the fp16 range whatever the magnitude of the activations
+            frag::scan_rows<NT, 4>(p.act, p.M, p.K, vec_ok, s_part, s_mx, s_rs);
+            if (tid < p.M) {
+                const float bm = s_mx[tid];
+                int ex = 15;
+                if (bm > 0.0f && isfinite(bm)) (void)frexpf(bm, &ex);   // bm = f * 2^ex, f in [0.5, 1)
+                const int e = max(-120, min(120, 15 - ex));
+                s_up[tid] = ldexpf(1.0f, e);
+                s_dq[tid] = ldexpf(1.0f, -e);
+            }
         }
         __syncthreads();  // previous pass fully consumed (and the fills above are done)
         // ---- stage activations [M][k0, k0+kc_len) as fp16 (hi | lo) ----------------------------
         // Work item of a warp = 32 groups of eight consecutive k of one batch row: two 16-byte loads
         // per lane, one 16-byte store per plane (an 8-group is contiguous in the staged order of every
-        // format), one warp reduction for the row sum.  Two items are in flight per warp.
-        if (has_zero) {
-            for (int m = lane; m < p.M; m += 32) s_rs_part[warp * 64 + m] = 0.0f;
-            __syncwarp();
-        }
+        // format).  Two items are in flight per warp.
         if (vec_ok) {
             const int chunks = kc_len / 8, cg32 = (chunks + 31) / 32, witems = p.M * cg32;
             for (int w0 = warp; w0 < witems; w0 += 2 * NW) {
@@ -354,18 +317,16 @@ qmm_mma_kernel(MmaParams p) {
                     if (wi >= witems) break;   // warp-uniform
                     const float e[8] = {v[q][0].x, v[q][0].y, v[q][0].z, v[q][0].w,
                                         v[q][1].x, v[q][1].y, v[q][1].z, v[q][1].w};
-                    float sum = 0.0f, amax = 0.0f;
+                    const float up = s_up[mm[q]];
                     __align__(16) __half hi[8];
                     __align__(16) __half lo[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        sum += e[i];
-                        amax = fmaxf(amax, fabsf(e[i]));
+                        const float a = e[i] * up;
                         const int pos = FragTraits<FMT>::four_bit ? pos8<FMT>(i) : i;
-                        hi[pos] = __float2half_rn(e[i]);
-                        lo[pos] = __float2half_rn(e[i] - __half2float(hi[pos]));
+                        hi[pos] = __float2half_rn(a);
+                        lo[pos] = __float2half_rn(a - __half2float(hi[pos]));
                     }
-                    if (amax > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
                     if (cc[q] < chunks) {
                         const int base = act_pos<FMT>(cc[q] * 8) * 2;   // bytes; 8-groups stay together
                         *reinterpret_cast<uint4 *>(s_act + (size_t)mm[q] * RS + base) =
@@ -374,21 +335,14 @@ qmm_mma_kernel(MmaParams p) {
                             *reinterpret_cast<uint4 *>(s_act + (size_t)(p.M + mm[q]) * RS + base) =
                                 *reinterpret_cast<const uint4 *>(lo);
                     }
-                    if (has_zero) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-                        if (lane == 0) s_rs_part[warp * 64 + mm[q]] += sum;
-                    }
                 }
             }
         } else {
             for (int m = 0; m < p.M; ++m) {
                 const float *src = p.act + (size_t)m * p.K;
-                float part = 0.0f;
+                const float up = s_up[m];
                 for (int k = tid; k < kc_len; k += NT) {
-                    const float a = (k0 + k < p.K) ? __ldg(src + k0 + k) : 0.0f;
-                    part += a;
-                    if (fabsf(a) > 65000.0f) atomicOr(p.err_flag, 2);  // outside the fp16 range
+                    const float a = (k0 + k < p.K) ? __ldg(src + k0 + k) * up : 0.0f;
                     const __half h = __float2half_rn(a);
                     const int pos = act_pos<FMT>(k);
                     reinterpret_cast<__half *>(s_act + (size_t)m * RS)[pos] = h;
@@ -396,21 +350,11 @@ qmm_mma_kernel(MmaParams p) {
                         reinterpret_cast<__half *>(s_act + (size_t)(p.M + m) * RS)[pos] =
                             __float2half_rn(a - __half2float(h));
                 }
-                if (has_zero) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-                    if (lane == 0) s_rs_part[warp * 64 + m] += part;
-                }
             }
         }
         __syncthreads();
         // fused gather: the first poll of the previous step's words was issued before the staging
         if (CG == 1 && p.gather_on && k0 == 0 && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
-        if (has_zero && tid < p.M) {
-            float s = s_rs[tid];
-            for (int w = 0; w < NW; ++w) s += s_rs_part[w * 64 + tid];
-            s_rs[tid] = s;
-        }
 
         // ---- stream this K range of every tile of the group -------------------------------
         int c_st = 0;
@@ -420,14 +364,12 @@ qmm_mma_kernel(MmaParams p) {
             cp_async_wait<S - 1>();  // the current item has landed in this lane's ring
             const int ch = gw + j * kW;
             uint4 cur[kU][2];
-            float cur_bs[kU][2];
 #pragma unroll
             for (int u = 0; u < kU; ++u)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int slot = c_st * UNITS + u * 2 + h;
                     cur[u][h] = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
-                    cur_bs[u][h] = (FMT == FNN_FMT_I4CB) ? my_ring_bs[slot * 32] : 0.0f;
                 }
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
@@ -435,14 +377,6 @@ qmm_mma_kernel(MmaParams p) {
                 const int kb_s = min(kb, KBc - 1);
                 // byte offset of this lane's first B vector of the k-block in a staged row
                 const int voff = T::four_bit ? (kb_s * KBLK + c * 8) * 2 : (kb_s * KBLK + c * 16) * 2;
-                uint32_t bs2[2] = {0u, 0u};
-                if (FMT == FNN_FMT_I4CB) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        __half2 t = __float2half2_rn(cur_bs[u][h]);
-                        bs2[h] = *reinterpret_cast<uint32_t *>(&t);
-                    }
-                }
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     // A registers for the two MMAs this B vector feeds
@@ -450,17 +384,17 @@ qmm_mma_kernel(MmaParams p) {
                     if (T::four_bit) {
                         uint32_t wl = (v == 0) ? cur[u][0].x : (v == 1) ? cur[u][0].y : (v == 2) ? cur[u][0].z : cur[u][0].w;
                         uint32_t wh = (v == 0) ? cur[u][1].x : (v == 1) ? cur[u][1].y : (v == 2) ? cur[u][1].z : cur[u][1].w;
-                        MmaDec<FMT>::run(wl, alo, s_lut + lane, bs2[0]);
-                        MmaDec<FMT>::run(wh, ahi, s_lut + lane, bs2[1]);
+                        MmaDec<FMT>::run(wl, alo);
+                        MmaDec<FMT>::run(wh, ahi);
                     } else {
                         uint32_t wl0 = (v == 0) ? cur[u][0].x : cur[u][0].z;
                         uint32_t wl1 = (v == 0) ? cur[u][0].y : cur[u][0].w;
                         uint32_t wh0 = (v == 0) ? cur[u][1].x : cur[u][1].z;
                         uint32_t wh1 = (v == 0) ? cur[u][1].y : cur[u][1].w;
-                        MmaDec<FMT>::run(wl0, alo, nullptr, 0u);
-                        MmaDec<FMT>::run(wl1, alo + 2, nullptr, 0u);
-                        MmaDec<FMT>::run(wh0, ahi, nullptr, 0u);
-                        MmaDec<FMT>::run(wh1, ahi + 2, nullptr, 0u);
+                        MmaDec<FMT>::run(wl0, alo);
+                        MmaDec<FMT>::run(wl1, alo + 2);
+                        MmaDec<FMT>::run(wh0, ahi);
+                        MmaDec<FMT>::run(wh1, ahi + 2);
                     }
                     const int boff = voff + (T::four_bit ? v * 64 : v * 16);
 #pragma unroll
@@ -514,15 +448,11 @@ qmm_mma_kernel(MmaParams p) {
         };
         float dot = frag_at(m);
         if (p.split) dot += frag_at(Mh + m);
+        dot *= s_dq[m];   // power of two: exact
         const float *meta = my_meta + (tl * 16 + r16) * 3;
         const float bias = meta[2];
-        float r;
-        if (FMT == FNN_FMT_I4CB) {
-            r = apply_act(p.bias ? __fadd_rn(dot, bias) : dot, p.epilogue);
-        } else {
-            r = finish_output(dot, meta[0], meta[1], has_zero ? s_rs[m] : 0.0f, p.bias != nullptr,
-                              bias, p.epilogue);
-        }
+        const float r = finish_output(dot, meta[0], meta[1], has_zero ? s_rs[m] : 0.0f, p.bias != nullptr,
+                                      bias, p.epilogue);
         if (CG == 1 && p.gather_on)
             gather_store(p.g, gc.step, m, n, r);
         else
@@ -547,7 +477,29 @@ __global__ void to_frag_kernel(const uint4 *rows, size_t ld_u4, size_t N, size_t
     }
 }
 
-// I4CB block scales [N][bpr] -> fragment order (one scale per 16-byte unit)
+// Codebook format: the unit of lane (g, c) carries word c of each of the four 32-element scale blocks
+// of the k-block (a 4 x 4 transpose of 32-bit words inside every 64 bytes of a row), so that one
+// m16n8k32 MMA covers exactly one scale block.  No bit inside a word moves.
+__global__ void to_frag_cb_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t KB, size_t ntiles,
+                                  uint4 *frag) {
+    size_t total = ntiles * KB * 2 * 32;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        size_t lane = i & 31, h = (i >> 5) & 1, t = i >> 6;
+        size_t kb = t % KB, rt = t / KB;
+        size_t row = rt * 16 + h * 8 + (lane >> 2), c = lane & 3;
+        uint32_t v[4] = {0, 0, 0, 0};
+        if (row < N) {
+            for (size_t b = 0; b < 4; ++b) {
+                size_t word = (kb * 4 + b) * 4 + c;
+                if (word < ld_words) v[b] = rows[row * ld_words + word];
+            }
+        }
+        frag[i] = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// I4CB block scales [N][bpr] -> fragment order (the slot of lane (g, c) holds block kb*4 + c)
 __global__ void to_frag_scales_kernel(const float *scales, size_t bpr, size_t N, size_t KB,
                                       size_t ntiles, float *out) {
     size_t total = ntiles * KB * 2 * 32;
@@ -559,11 +511,6 @@ __global__ void to_frag_scales_kernel(const float *scales, size_t bpr, size_t N,
         size_t blk = kb * 4 + (lane & 3);
         out[i] = (row < N && blk < bpr) ? scales[row * bpr + blk] : 0.0f;
     }
-}
-
-template <int FMT>
-int kblk_of() {
-    return FragTraits<FMT>::KBLK;
 }
 
 int kblk_for(int fmt) {
@@ -581,7 +528,11 @@ int ensure_frag(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
     FNN_CUDA_CHECK(cudaMalloc((void **)&w->frag, units * sizeof(uint4)), FNN_ERR_MEMORY);
     w->frag_bytes = units * sizeof(uint4);
     int blocks = (int)std::min<size_t>(div_ceil(units, 256), (size_t)ctx->sm_count * 16);
-    to_frag_kernel<<<blocks, 256, 0, ctx->stream>>>(w->rows, w->ld_u4, w->N, KB, ntiles, w->frag);
+    if (w->fmt == FNN_FMT_I4CB)
+        to_frag_cb_kernel<<<blocks, 256, 0, ctx->stream>>>((const uint32_t *)w->rows, w->ld_u4 * 4, w->N, KB,
+                                                         ntiles, w->frag);
+    else
+        to_frag_kernel<<<blocks, 256, 0, ctx->stream>>>(w->rows, w->ld_u4, w->N, KB, ntiles, w->frag);
     FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
     ctx->launches++;
     if (w->fmt == FNN_FMT_I4CB) {
@@ -600,14 +551,11 @@ int launch_mma_g(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *o
     const fnn_cuda_qweight *w = a.w;
     MmaParams p{};
     p.frag = w->frag;
-    p.frag_bs = w->frag_bs;
     p.scales = w->scales;
     p.zeros = w->zeros;
-    p.codebook = w->codebook;
     p.act = act;
     p.out = out;
     p.bias = a.bias;
-    p.err_flag = ctx->err_flag;
     p.M = M;
     p.N = (int)w->N;
     p.K = (int)w->K;
@@ -619,36 +567,21 @@ int launch_mma_g(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *o
     if (p.gather_on) p.g = *a.gather;
 
     // One block per SM: weight ring + as much of K as fits beside the reduction buffers.
-    const int Kpad = p.KB * T::KBLK;
     const int act_rows = split ? 2 * M : M;
-    const size_t lut = (FMT == FNN_FMT_I4CB) ? 256 * 32 * 4 : 0;
-    const size_t ring = (size_t)G * kW * stages_for(CG) * kU * 2 * (512 + (FMT == FNN_FMT_I4CB ? 128 : 0));
-    const size_t fixed = ring + (size_t)(G * 2 * kW * CG * 128 + G * kW * 64 + 64) * 4 + lut;
+    const int Mr = (M + 3) & ~3;
+    const size_t ring = (size_t)G * kW * stages_for(CG) * kU * 2 * 512;
+    const size_t fixed = ring + (size_t)(G * 2 * kW * CG * 128 + G * kW * Mr * 2 + 4 * Mr) * 4;
     const size_t per_tile = (size_t)G * (CG * 512 + 192);  // output accumulator + row metadata
-    const size_t cap = 226 * 1024;
-    // one block per SM whenever the per-group accumulators of ceil(tiles / groups) tiles fit next to
-    // at least one ring chunk of activations; otherwise more blocks, run in waves
-    const size_t min_act = (size_t)act_rows * (2 * T::KBLK * kU + T::PAD_BYTES);
-    FNN_REQUIRE(fixed + per_tile + min_act <= cap, FNN_ERR_UNSUPPORTED,
+    frag::FragSizing sz;
+    const bool fits = frag::size_frag_launch(
+        ctx->sm_count, p.ntiles, G, p.KB * T::KBLK, T::KBLK, fixed, per_tile,
+        [&](int kc) { return (size_t)act_rows * (2 * kc + T::PAD_BYTES); }, &sz);
+    FNN_REQUIRE(fits, FNN_ERR_UNSUPPORTED,
                 "qmatmul: shared memory budget exceeded for M=%d on the skinny tensor-core path", M);
-    int grid = ctx->sm_count;
-    int tpg = (int)div_ceil((size_t)p.ntiles, (size_t)grid * G);
-    const int tpg_max = (int)((cap - fixed - min_act) / per_tile);
-    if (tpg > tpg_max) {
-        tpg = tpg_max;
-        grid = (int)div_ceil((size_t)p.ntiles, (size_t)G * tpg);
-    }
-    if (tpg < 1) tpg = 1;
-    grid = (int)std::min<size_t>((size_t)grid, div_ceil((size_t)p.ntiles, (size_t)G));
-    p.tiles_per_group = tpg;
-    const size_t act_budget = cap - fixed - (size_t)tpg * per_tile;
-    int Kc = Kpad;
-    while ((size_t)act_rows * (2 * Kc + T::PAD_BYTES) > act_budget && Kc > T::KBLK * kU) {
-        Kc = (Kc / 2 + T::KBLK - 1) / T::KBLK * T::KBLK;
-    }
-    p.Kc = Kc;
-    const size_t act_bytes = (size_t)act_rows * (2 * Kc + T::PAD_BYTES);
-    const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
+    p.tiles_per_group = sz.tiles_per_group;
+    p.Kc = sz.Kc;
+    const size_t smem = sz.smem;
+    const int grid = sz.grid;
     auto kern = qmm_mma_kernel<FMT, CG, G>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
@@ -662,7 +595,7 @@ int launch_mma_g(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *o
 // tiles run fewer groups per block so that the tiles spread over more SMs.
 template <int FMT, int CG>
 int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out, int M, int split) {
-    constexpr int GMAX = groups_for(FMT, CG);
+    constexpr int GMAX = groups_for(CG);
     if (CG == 1) {
         const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
         if (GMAX >= 3 && (ntiles + 2) / 3 >= want) return launch_mma_g<FMT, CG, GMAX>(ctx, a, act, out, M, split);
@@ -675,20 +608,22 @@ int launch_mma(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *out
 template <int FMT>
 int launch_mma_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const size_t N = a.w->N, K = a.w->K;
-    for (size_t m0 = 0; m0 < a.M; m0 += 64) {
-        const int M = (int)std::min<size_t>(64, a.M - m0);
+    for (size_t m0 = 0; m0 < a.M; m0 += kMaxRows) {
+        const int M = (int)std::min<size_t>(kMaxRows, a.M - m0);
         const float *act = a.a + m0 * K;
         float *out = a.out + m0 * N;
         int rc;
-        // two-term fp16 activations while the batch fits one 8-column group (M <= 4), one term after
+        // two-term fp16 activations (f32-grade results) up to 32 batch rows: the hi and lo terms of a
+        // row are two of the 8 * CG MMA columns; one term beyond, where the tcgen05 kernel is the
+        // intended path and this one only runs on request
         if (M <= 4)
             rc = launch_mma<FMT, 1>(ctx, a, act, out, M, 1);
         else if (M <= 8)
-            rc = launch_mma<FMT, 1>(ctx, a, act, out, M, 0);
+            rc = launch_mma<FMT, 2>(ctx, a, act, out, M, 1);
         else if (M <= 16)
-            rc = launch_mma<FMT, 2>(ctx, a, act, out, M, 0);
+            rc = launch_mma<FMT, 4>(ctx, a, act, out, M, 1);
         else if (M <= 32)
-            rc = launch_mma<FMT, 4>(ctx, a, act, out, M, 0);
+            rc = launch_mma<FMT, 8>(ctx, a, act, out, M, 1);
         else
             rc = launch_mma<FMT, 8>(ctx, a, act, out, M, 0);
         if (rc != FNN_OK) return rc;
@@ -701,7 +636,7 @@ int launch_mma_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
 
 bool qmm_mma_supported(const fnn_cuda_qweight *w, size_t M) {
     (void)M;
-    return w->N < (1u << 27) && w->K < (1u << 27) && w->mma_ok;
+    return w->N < (1u << 27) && w->K < (1u << 27);
 }
 
 int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) { return ensure_frag(ctx, w); }
@@ -709,9 +644,9 @@ int prepare_qmm_mma(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) { return ensure_frag
 int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     int rc = ensure_frag(ctx, const_cast<fnn_cuda_qweight *>(a.w));
     if (rc != FNN_OK) return rc;
-    // up to four batch rows the 8-bit operand kernel serves I8 / I4 / FP4 from the same fragment layout
-    // with far fewer instructions per weight; the fp16 kernel below serves FP8, the codebook format
-    // and larger batches
+    // up to sixteen batch rows the 8-bit operand kernel serves I8 / I4 / FP4 / the codebook format from
+    // the same fragment layout with exact integer products; the fp16 kernel below serves FP8 and larger
+    // batches
     if (qmm_mma8_supported(a.w, a.M)) return launch_qmm_mma8(ctx, a);
     switch (a.w->fmt) {
     case FNN_FMT_I8:
@@ -723,7 +658,17 @@ int launch_qmm_mma(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     case FNN_FMT_F4:
         return launch_mma_fmt<FNN_FMT_F4>(ctx, a);
     case FNN_FMT_I4CB:
-        return launch_mma_fmt<FNN_FMT_I4CB>(ctx, a);
+        // block scales inside K: only the 8-bit operand kernel carries them; larger batches run
+        // through it sixteen rows at a time
+        for (size_t m0 = 0; m0 < a.M; m0 += 16) {
+            QmmArgs part = a;
+            part.a = a.a + m0 * a.w->K;
+            part.out = a.out + m0 * a.w->N;
+            part.M = std::min<size_t>(16, a.M - m0);
+            rc = launch_qmm_mma8(ctx, part);
+            if (rc != FNN_OK) return rc;
+        }
+        return FNN_OK;
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: unknown format %d", a.w->fmt);
 }

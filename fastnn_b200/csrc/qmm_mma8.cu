@@ -1,4 +1,4 @@
-// Skinny-M kernel (1 <= M <= 4) on 8-bit tensor-core operands: the HBM scan of the weights with
+// Skinny-M kernel (1 <= M <= 16) on 8-bit tensor-core operands: the HBM scan of the weights with
 // almost no instruction per weight.
 //
 // Same skeleton as the fp16 fragment kernel (fragment-major weights, one block per SM, groups of
@@ -8,46 +8,39 @@
 //   I4   -> s8 operands holding 16*q: two masks per word of eight codes
 //   FP4  -> s8 operands holding 2*|v| through a byte-permute table, positive and negative codes
 //           in separate operands (two accumulators, subtracted at the end): no sign arithmetic
+//   I4CB -> the 16 centroids as 14-bit fixed point, 128*hi + lo with hi, lo in [0, 127], looked up from
+//           two byte-permute tables with the raw index as selector (two operands, two MMAs per
+//           32-element scale block); the block scale multiplies the block's exact integer sum in f32
 // (FP8 is not served here: `mma.sync` with e4m3 operands measured slower than the fp16 kernel on this
 // part) and the f32 activations are rewritten while they are staged, per batch row, as
 //   a ~= dq * (128*hi + lo)        (15-bit fixed point, exact int32 accumulation)
 // Partial sums are integers, so the split-K reduction is exact in any order.
 // Epilogue as everywhere:  out = act(dq*acc*scale[n] + zero[n]*sum_k a[m,k] + bias[n])
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
-#include "common.cuh"
-
-#include <algorithm>
+#include "frag_common.cuh"
 
 namespace fnn {
 
 namespace {
 
-constexpr int kW8 = 8;   // warps per group
-constexpr int kU8 = 2;   // k-blocks per ring chunk
+using frag::cp_async_commit;
+using frag::cp_async_wait;
+using frag::group_barrier;
+
+constexpr int kW8 = frag::kWarpsPerGroup;   // warps per group
+constexpr int kU8 = frag::kChunkBlocks;     // k-blocks per ring chunk
 constexpr int kS8 = 3;   // ring stages per lane (two chunks, 96 KB per SM, in flight)
-constexpr int kG8Max = 3;   // groups per block (fewer when a layer has too few row tiles to fill the SMs)
+constexpr int kMma8MaxRows = 16;   // four 8-column groups of (term, batch row) columns
 
 template <int FMT>
 struct T8 {
-    static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4);
+    static constexpr bool four_bit = (FMT == FNN_FMT_I4 || FMT == FNN_FMT_F4 || FMT == FNN_FMT_I4CB);
+    static constexpr bool codebook = (FMT == FNN_FMT_I4CB);
     static constexpr int KBLK = four_bit ? 128 : 64;       // k per k-block (4 lanes x 16 bytes per row)
     static constexpr int MMAS = four_bit ? 4 : 2;          // m16n8k32 MMAs per k-block
     static constexpr int PAD = four_bit ? 16 : 64;         // activation row padding (bank spread)
 };
 
-__device__ __forceinline__ void group_barrier8(int group) {
-    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kW8 * 32) : "memory");
-}
-__device__ __forceinline__ void cp16(void *dst, const void *src, int src_bytes) {
-    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 __device__ __forceinline__ void mma_s8(int *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
@@ -87,6 +80,23 @@ __device__ __forceinline__ void decode_f4(uint32_t w, uint32_t &plo, uint32_t &p
     nhi = prmt(t0, t1, f >> 16);
 }
 
+//   I4CB (index into 16 centroids): every centroid is carried as v = 128*hi + lo, hi and lo in
+//   [0, 127], so a table byte never has its top bit set.  Indices 0..7 come out of one prmt on the
+//   raw word (indices 8..15 select "replicated top bit" = 0 there), indices 8..15 out of a second
+//   prmt on the word with every index's bit 3 flipped, and the two are OR-ed.
+struct CbTables {
+    uint32_t hi[4], lo[4];   // bytes of entries 0-3, 4-7, 8-11, 12-15
+};
+__device__ __forceinline__ void decode_cb(const CbTables &t, uint32_t w, uint32_t &h0, uint32_t &h1,
+                                          uint32_t &l0, uint32_t &l1) {
+    const uint32_t f = w ^ 0x88888888u, w16 = w >> 16, f16 = f >> 16;
+    h0 = prmt(t.hi[0], t.hi[1], w) | prmt(t.hi[2], t.hi[3], f);       // codes 0..3 of the word
+    h1 = prmt(t.hi[0], t.hi[1], w16) | prmt(t.hi[2], t.hi[3], f16);   // codes 4..7
+    l0 = prmt(t.lo[0], t.lo[1], w) | prmt(t.lo[2], t.lo[3], f);
+    l1 = prmt(t.lo[0], t.lo[1], w16) | prmt(t.lo[2], t.lo[3], f16);
+}
+constexpr int kCbHalf = 8192;   // centroid c is carried as v = round(c / cmax * 8191) + 8192
+
 // Staged byte position of activation k inside its row.
 template <int FMT>
 __device__ __forceinline__ int act_pos8(int k) {
@@ -99,6 +109,8 @@ __device__ __forceinline__ int act_pos8(int k) {
 
 struct P8 {
     const uint4 *frag;
+    const float *frag_bs;   // I4CB: block scales in fragment order
+    const float *codebook;  // I4CB: 16 centroids
     const float *scales;
     const float *zeros;
     const float *act;
@@ -113,7 +125,7 @@ struct P8 {
 };
 
 // MULTI: more than one batch row (all rows scanned and staged together); the single-row instantiation
-// keeps the shortest prologue.
+// keeps the shortest prologue.  CG 8-column groups hold the (term, batch row) columns: up to 4 * CG rows.
 template <int FMT, int CG, int kG8, bool MULTI>
 __global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
 qmm_mma8_kernel(P8 p) {
@@ -121,17 +133,23 @@ qmm_mma8_kernel(P8 p) {
     constexpr int KBLK = TT::KBLK, MMAS = TT::MMAS;
     constexpr int NT = kG8 * kW8 * 32, NW = kG8 * kW8;
     constexpr int UNITS = kU8 * 2;
+    constexpr int MR = 4 * CG;                 // batch rows this instantiation can hold
     extern __shared__ __align__(16) unsigned char smem[];
     const int RS = p.Kc + TT::PAD;             // bytes per staged activation row
     const int cols = 2 * p.M;                  // (term, batch row) columns in use
+    constexpr bool CB = TT::codebook;
     unsigned char *s_ring = smem;                                         // [NW][S][UNITS][32] uint4
-    unsigned char *s_act = s_ring + (size_t)NW * kS8 * UNITS * 512;       // [cols][RS]
+    float *s_ring_bs = reinterpret_cast<float *>(s_ring + (size_t)NW * kS8 * UNITS * 512);   // I4CB: [NW][S][UNITS][32]
+    unsigned char *s_act = reinterpret_cast<unsigned char *>(s_ring_bs + (CB ? (size_t)NW * kS8 * UNITS * 32 : 0));  // [cols][RS]
     float *s_red = reinterpret_cast<float *>(s_act + (((size_t)cols * RS + 15) & ~(size_t)15));
     float *s_out = s_red + kG8 * 2 * kW8 * CG * 128;                      // [G][tiles_per_group][CG*128]
     float *s_meta = s_out + (size_t)kG8 * p.tiles_per_group * CG * 128;   // [G][tiles_per_group][16][3]
-    float *s_part = s_meta + (size_t)kG8 * p.tiles_per_group * 48;        // [NW][2]
-    float *s_dq = s_part + NW * (MULTI ? 8 : 2);   // s_part: [NW][rows (4 when MULTI)][2]                                        // [8]
-    float *s_rs = s_dq + 8;                                               // [8]
+    float *s_part = s_meta + (size_t)kG8 * p.tiles_per_group * 48;        // [NW][MR][2]
+    float *s_dq = s_part + NW * MR * 2;                                   // [MR]
+    float *s_rs = s_dq + MR;                                              // [MR]
+    float *s_mx = s_rs + MR;                                              // [MR]
+    // I4CB: -8192 * (sum of the staged bytes of a 32-element block), per block and column
+    int *s_boff = reinterpret_cast<int *>(s_mx + MR);                     // [Kc / 32][8 * CG]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = warp / kW8, gw = warp % kW8, gtid = tid - group * kW8 * 32;
@@ -147,11 +165,32 @@ qmm_mma8_kernel(P8 p) {
     float *my_red = s_red + (size_t)group * 2 * kW8 * CG * 128;
     float *my_meta = s_meta + (size_t)group * p.tiles_per_group * 48;
     unsigned char *my_ring = s_ring + (size_t)warp * kS8 * UNITS * 512 + lane * 16;
+    float *my_ring_bs = s_ring_bs + (size_t)warp * kS8 * UNITS * 32;
+
+    // I4CB: the centroids as 14-bit fixed point (every thread builds its own copy of the two tables)
+    CbTables cbt{};
+    float cb_unit = 0.0f;   // value of one fixed-point step
+    if (CB) {
+        float cv[16], cmax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            cv[j] = __ldg(p.codebook + j);
+            cmax = fmaxf(cmax, fabsf(cv[j]));
+        }
+        const float to_fix = cmax > 0.0f ? (float)(kCbHalf - 1) / cmax : 0.0f;
+        cb_unit = cmax / (float)(kCbHalf - 1);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int v = __float2int_rn(cv[j] * to_fix) + kCbHalf;   // 1 .. 16383
+            cbt.hi[j >> 2] |= (uint32_t)(v >> 7) << ((j & 3) * 8);
+            cbt.lo[j >> 2] |= (uint32_t)(v & 127) << ((j & 3) * 8);
+        }
+    }
 
     for (int i = gtid; i < tiles_here * 16; i += kW8 * 32) {
         const int n = (gg + (i >> 4) * GG) * 16 + (i & 15);
         const bool in = n < p.N;
-        my_meta[i * 3 + 0] = in ? __ldg(p.scales + n) : 1.0f;
+        my_meta[i * 3 + 0] = (in && !CB) ? __ldg(p.scales + n) : 1.0f;
         my_meta[i * 3 + 1] = (in && has_zero) ? __ldg(p.zeros + n) : 0.0f;
         my_meta[i * 3 + 2] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
     }
@@ -162,13 +201,15 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg) brow[cg] = (cg * 8 + g < cols) ? cg * 8 + g : -1;
 
-    int acci[CG][4], accn[CG][4];   // accn: FP4's negative-weight sums
+    int acci[CG][4], accn[FMT == FNN_FMT_F4 ? CG : 1][4];   // accn: FP4's negative-weight sums
+    float accf[CB ? CG : 1][4];                              // I4CB: block sums times block scales
 #pragma unroll
     for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             acci[cg][r] = 0;
-            accn[cg][r] = 0;
+            if (FMT == FNN_FMT_F4) accn[cg][r] = 0;
+            if constexpr (CB) accf[cg][r] = 0.0f;
         }
     int red_buf = 0;
 
@@ -191,10 +232,15 @@ qmm_mma8_kernel(P8 p) {
                 const int kb = ch * kU8 + u;
                 const bool ok = valid && (kb < KBc);
                 const uint4 *src = ok ? tile_src + (size_t)kb * 64 : p.frag;
-                cp16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
-                cp16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
+                frag::cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2) * 512, src, ok ? 16 : 0);
+                frag::cp_async16(my_ring + (size_t)(i_st * UNITS + u * 2 + 1) * 512, src + 32, ok ? 16 : 0);
+                if (CB) {   // one block scale per 16-byte unit
+                    const float *bsrc = p.frag_bs + (ok ? (src - p.frag) : 0);
+                    frag::cp_async4(my_ring_bs + (i_st * UNITS + u * 2) * 32 + lane, bsrc, ok ? 4 : 0);
+                    frag::cp_async4(my_ring_bs + (i_st * UNITS + u * 2 + 1) * 32 + lane, bsrc + 32, ok ? 4 : 0);
+                }
             }
-            cp_commit();
+            cp_async_commit();
             if (++i_j == cpw) {
                 i_j = 0;
                 ++i_tl;
@@ -210,99 +256,11 @@ qmm_mma8_kernel(P8 p) {
             pdl_wait();
             if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
             // ---- per-row step and sum: max |a| over the whole row first ---------------------
-            if (MULTI) {
-                // all rows in one pass over the activations: one barrier pair instead of one per row
-                float mx[4], sum[4];
-#pragma unroll
-                for (int m = 0; m < 4; ++m) mx[m] = sum[m] = 0.0f;
-                if (vec_ok) {
-                    for (int i = tid; i < p.K / 4; i += NT) {
-#pragma unroll
-                        for (int m = 0; m < 4; ++m) {
-                            if (m < p.M) {
-                                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.act + (size_t)m * p.K) + i);
-                                mx[m] = fmaxf(fmaxf(mx[m], fmaxf(fabsf(v.x), fabsf(v.y))),
-                                              fmaxf(fabsf(v.z), fabsf(v.w)));
-                                sum[m] += (v.x + v.y) + (v.z + v.w);
-                            }
-                        }
-                    }
-                } else {
-                    for (int k = tid; k < p.K; k += NT) {
-#pragma unroll
-                        for (int m = 0; m < 4; ++m) {
-                            if (m < p.M) {
-                                const float a = __ldg(p.act + (size_t)m * p.K + k);
-                                mx[m] = fmaxf(mx[m], fabsf(a));
-                                sum[m] += a;
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    if (m < p.M) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) {
-                            mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xFFFFFFFFu, mx[m], o));
-                            sum[m] += __shfl_xor_sync(0xFFFFFFFFu, sum[m], o);
-                        }
-                        if (lane == 0) {
-                            s_part[(warp * 4 + m) * 2] = mx[m];
-                            s_part[(warp * 4 + m) * 2 + 1] = sum[m];
-                        }
-                    }
-                }
-                __syncthreads();
-                if (tid < p.M) {   // one thread per row folds the warps' partials in a fixed order
-                    float bm = 0.0f, bs = 0.0f;
-                    for (int w = 0; w < NW; ++w) {
-                        bm = fmaxf(bm, s_part[(w * 4 + tid) * 2]);
-                        bs += s_part[(w * 4 + tid) * 2 + 1];
-                    }
-                    s_dq[tid] = (bm > 0.0f && isfinite(bm)) ? bm / 16256.0f : 1.0f;
-                    s_rs[tid] = bs;
-                }
-                __syncthreads();
-            } else
-            for (int m = 0; m < p.M; ++m) {
-                const float *row = p.act + (size_t)m * p.K;
-                float mx = 0.0f, sum = 0.0f;
-                if (vec_ok) {
-                    for (int i = tid; i < p.K / 4; i += NT) {
-                        const float4 v = __ldg(reinterpret_cast<const float4 *>(row) + i);
-                        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-                        sum += (v.x + v.y) + (v.z + v.w);
-                    }
-                } else {
-                    for (int k = tid; k < p.K; k += NT) {
-                        const float a = __ldg(row + k);
-                        mx = fmaxf(mx, fabsf(a));
-                        sum += a;
-                    }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-                }
-                if (lane == 0) {
-                    s_part[warp * 2] = mx;
-                    s_part[warp * 2 + 1] = sum;
-                }
-                __syncthreads();
-                if (tid == 0) {
-                    float bm = 0.0f, bs = 0.0f;
-                    for (int w = 0; w < NW; ++w) {
-                        bm = fmaxf(bm, s_part[w * 2]);
-                        bs += s_part[w * 2 + 1];
-                    }
-                    const float full = 16256.0f;
-                    s_dq[m] = (bm > 0.0f && isfinite(bm)) ? bm / full : 1.0f;
-                    s_rs[m] = bs;
-                }
-                __syncthreads();
-            }
+            frag::scan_rows<NT, MULTI ? 4 : 1>(p.act, p.M, p.K, vec_ok, s_part, s_mx, s_rs);
+            if (tid < p.M) {
+                const float bm = s_mx[tid];
+                s_dq[tid] = (bm > 0.0f && isfinite(bm)) ? bm / 16256.0f : 1.0f;
+            }   // (published by the barrier below)
 
             // the first poll of the previous step's words was issued at the top; its latency is hidden by now
             if (p.gather_on && gc.step > 1u) gather_check_prev(p.g, gc, gridDim.x * NT);
@@ -311,39 +269,43 @@ qmm_mma8_kernel(P8 p) {
         __syncthreads();  // previous pass fully consumed
         // ---- stage the activation bytes of [k0, k0 + kc_len) --------------------------------
         if (MULTI && vec_ok && (p.K % 8 == 0)) {
-            // eight activations of every row per thread and step: two 16-byte loads per row in flight,
+            // eight activations of four rows per thread and step: two 16-byte loads per row in flight,
             // one 8-byte store per (row, plane)
             const int n8 = kc_len / 8;
             for (int i8 = tid; i8 < n8; i8 += NT) {
                 const bool in = k0 + i8 * 8 < p.K;
-                float4 v[4][2];
+                for (int mb = 0; mb < p.M; mb += 4) {
+                    float4 v[4][2];
 #pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    v[m][0] = v[m][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (m < p.M && in) {
-                        const float4 *src = reinterpret_cast<const float4 *>(p.act + (size_t)m * p.K + k0 + i8 * 8);
-                        v[m][0] = __ldg(src);
-                        v[m][1] = __ldg(src + 1);
-                    }
-                }
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    if (m < p.M) {
-                        const float inv = 1.0f / s_dq[m];
-                        const float e[8] = {v[m][0].x, v[m][0].y, v[m][0].z, v[m][0].w,
-                                            v[m][1].x, v[m][1].y, v[m][1].z, v[m][1].w};
-                        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            int q = __float2int_rn(e[j] * inv);
-                            q = max(-16256, min(16256, q));
-                            const int h = (q + 64) >> 7;
-                            const int pos = act_pos8<FMT>(j);   // position inside the 8-group
-                            hi[pos >> 2] |= (uint32_t)(h & 0xFF) << ((pos & 3) * 8);
-                            lo[pos >> 2] |= (uint32_t)((q - h * 128) & 0xFF) << ((pos & 3) * 8);
+                    for (int m = 0; m < 4; ++m) {
+                        v[m][0] = v[m][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (mb + m < p.M && in) {
+                            const float4 *src =
+                                reinterpret_cast<const float4 *>(p.act + (size_t)(mb + m) * p.K + k0 + i8 * 8);
+                            v[m][0] = __ldg(src);
+                            v[m][1] = __ldg(src + 1);
                         }
-                        *reinterpret_cast<uint2 *>(s_act + (size_t)m * RS + i8 * 8) = make_uint2(hi[0], hi[1]);
-                        *reinterpret_cast<uint2 *>(s_act + (size_t)(p.M + m) * RS + i8 * 8) = make_uint2(lo[0], lo[1]);
+                    }
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        if (mb + m < p.M) {
+                            const float inv = 1.0f / s_dq[mb + m];
+                            const float e[8] = {v[m][0].x, v[m][0].y, v[m][0].z, v[m][0].w,
+                                                v[m][1].x, v[m][1].y, v[m][1].z, v[m][1].w};
+                            uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                int q = __float2int_rn(e[j] * inv);
+                                q = max(-16256, min(16256, q));
+                                const int h = (q + 64) >> 7;
+                                const int pos = act_pos8<FMT>(j);   // position inside the 8-group
+                                hi[pos >> 2] |= (uint32_t)(h & 0xFF) << ((pos & 3) * 8);
+                                lo[pos >> 2] |= (uint32_t)((q - h * 128) & 0xFF) << ((pos & 3) * 8);
+                            }
+                            *reinterpret_cast<uint2 *>(s_act + (size_t)(mb + m) * RS + i8 * 8) = make_uint2(hi[0], hi[1]);
+                            *reinterpret_cast<uint2 *>(s_act + (size_t)(p.M + mb + m) * RS + i8 * 8) =
+                                make_uint2(lo[0], lo[1]);
+                        }
                     }
                 }
             }
@@ -387,13 +349,36 @@ qmm_mma8_kernel(P8 p) {
             }
         }
         __syncthreads();
+        if (CB) {
+            // -8192 * sum of each 32-element block of every staged column: the centroids are carried
+            // with an offset of 8192, which the second MMA of a block takes back through its C operand
+            const int nblk = kc_len / 32;
+            for (int i = tid; i < nblk * 8 * CG; i += NT) {
+                const int blk = i / (8 * CG), col = i - blk * (8 * CG);
+                int sum = 0;
+                if (col < cols) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(s_act + (size_t)col * RS + blk * 32);
+                    const uint4 x = src[0], y = src[1];
+                    sum = __dp4a((int)x.x, 0x01010101, sum);
+                    sum = __dp4a((int)x.y, 0x01010101, sum);
+                    sum = __dp4a((int)x.z, 0x01010101, sum);
+                    sum = __dp4a((int)x.w, 0x01010101, sum);
+                    sum = __dp4a((int)y.x, 0x01010101, sum);
+                    sum = __dp4a((int)y.y, 0x01010101, sum);
+                    sum = __dp4a((int)y.z, 0x01010101, sum);
+                    sum = __dp4a((int)y.w, 0x01010101, sum);
+                }
+                s_boff[i] = -kCbHalf * sum;
+            }
+            __syncthreads();
+        }
 
         // ---- stream this K range of every tile of the group ----------------------------------
         int c_st = 0;
         for (int tl = 0; tl < tiles_here; ++tl)
         for (int j = 0; j < cpw; ++j) {
             issue_next();
-            cp_wait<kS8 - 1>();
+            cp_async_wait<kS8 - 1>();
             const int ch = gw + j * kW8;
 #pragma unroll
             for (int u = 0; u < kU8; ++u) {
@@ -401,6 +386,38 @@ qmm_mma8_kernel(P8 p) {
                 const uint4 wl = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
                 const uint4 wh = *reinterpret_cast<const uint4 *>(my_ring + (size_t)(slot + 1) * 512);
                 const int kb_s = min(ch * kU8 + u, KBc - 1);
+                if constexpr (CB) {
+                    // The unit of lane (g, c) holds word c of the four 32-element blocks of this
+                    // k-block: block b is one MMA (hi operand) plus one (lo operand), eight codes of
+                    // rows g and g + 8 per lane, and its integer sum is scaled by the block scale of
+                    // each row, which sits in the ring slot of lane (g, b).
+                    const uint32_t wl4[4] = {wl.x, wl.y, wl.z, wl.w}, wh4[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        uint32_t ah[4], al[4];
+                        decode_cb(cbt, wl4[b], ah[0], ah[2], al[0], al[2]);   // row g
+                        decode_cb(cbt, wh4[b], ah[1], ah[3], al[1], al[3]);   // row g + 8
+                        const float bs_lo = my_ring_bs[slot * 32 + (lane & ~3) + b];
+                        const float bs_hi = my_ring_bs[(slot + 1) * 32 + (lane & ~3) + b];
+                        const int blk = kb_s * 4 + b;
+#pragma unroll
+                        for (int cg = 0; cg < CG; ++cg) {
+                            uint2 bb = make_uint2(0, 0);
+                            if (brow[cg] >= 0)
+                                bb = *reinterpret_cast<const uint2 *>(s_act + (size_t)brow[cg] * RS + blk * 32 + c * 8);
+                            const int2 off = *reinterpret_cast<const int2 *>(s_boff + blk * 8 * CG + cg * 8 + 2 * c);
+                            int dh[4] = {0, 0, 0, 0};
+                            int dl[4] = {off.x, off.y, off.x, off.y};
+                            mma_s8(dh, ah[0], ah[1], ah[2], ah[3], bb.x, bb.y);
+                            mma_s8(dl, al[0], al[1], al[2], al[3], bb.x, bb.y);
+                            accf[cg][0] = fmaf(bs_lo, (float)(dh[0] * 128 + dl[0]), accf[cg][0]);
+                            accf[cg][1] = fmaf(bs_lo, (float)(dh[1] * 128 + dl[1]), accf[cg][1]);
+                            accf[cg][2] = fmaf(bs_hi, (float)(dh[2] * 128 + dl[2]), accf[cg][2]);
+                            accf[cg][3] = fmaf(bs_hi, (float)(dh[3] * 128 + dl[3]), accf[cg][3]);
+                        }
+                    }
+                    continue;
+                }
                 // this lane's activation bytes of the k-block: 16 (8-bit codes) or 32 (4-bit)
                 const int boff = kb_s * KBLK + c * (KBLK / 4);
 #pragma unroll
@@ -433,8 +450,8 @@ qmm_mma8_kernel(P8 p) {
                         mma_s8(acci[cg], a[0][0], a[0][1], a[0][2], a[0][3], b.x, b.y);
                         mma_s8(acci[cg], a[1][0], a[1][1], a[1][2], a[1][3], b.z, b.w);
                         if (FMT == FNN_FMT_F4) {
-                            mma_s8(accn[cg], an[0][0], an[0][1], an[0][2], an[0][3], b.x, b.y);
-                            mma_s8(accn[cg], an[1][0], an[1][1], an[1][2], an[1][3], b.z, b.w);
+                            mma_s8(accn[FMT == FNN_FMT_F4 ? cg : 0], an[0][0], an[0][1], an[0][2], an[0][3], b.x, b.y);
+                            mma_s8(accn[FMT == FNN_FMT_F4 ? cg : 0], an[1][0], an[1][1], an[1][2], an[1][3], b.z, b.w);
                         }
                     }
                 }
@@ -448,11 +465,14 @@ qmm_mma8_kernel(P8 p) {
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         red[(gw * CG + cg) * 128 + r * 32 + lane] =
-                            (float)(FMT == FNN_FMT_F4 ? acci[cg][r] - accn[cg][r] : acci[cg][r]);
+                            CB ? accf[CB ? cg : 0][r]
+                               : (float)(FMT == FNN_FMT_F4 ? acci[cg][r] - accn[FMT == FNN_FMT_F4 ? cg : 0][r]
+                                                           : acci[cg][r]);
                         acci[cg][r] = 0;
-                        accn[cg][r] = 0;
+                        if (FMT == FNN_FMT_F4) accn[cg][r] = 0;
+                        if constexpr (CB) accf[cg][r] = 0.0f;
                     }
-                group_barrier8(group);
+                group_barrier(group);
                 for (int e = gtid; e < CG * 128; e += kW8 * 32) {
                     float s = 0.0f;
 #pragma unroll
@@ -462,7 +482,7 @@ qmm_mma8_kernel(P8 p) {
                 red_buf ^= 1;
             }
         }
-        cp_wait<0>();
+        cp_async_wait<0>();
     }
     __syncthreads();
     const unsigned step = gc.step;
@@ -483,8 +503,14 @@ qmm_mma8_kernel(P8 p) {
         if (FMT == FNN_FMT_I4) acc *= 0.0625f;  // operands carried 16*q
         if (FMT == FNN_FMT_F4) acc *= 0.5f;     // operands carried 2*|v|
         const float *meta = my_meta + (tl * 16 + r16) * 3;
-        const float v = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f,
-                                      p.bias != nullptr, meta[2], p.epilogue);
+        float v;
+        if (CB) {   // no per-row scale or zero point: the block scales are inside acc
+            const float dot = acc * s_dq[m] * cb_unit;
+            v = apply_act(p.bias ? __fadd_rn(dot, meta[2]) : dot, p.epilogue);
+        } else {
+            v = finish_output(acc * s_dq[m], meta[0], meta[1], has_zero ? s_rs[m] : 0.0f, p.bias != nullptr,
+                              meta[2], p.epilogue);
+        }
         if (!p.gather_on) {
             p.out[(size_t)m * p.N + n] = v;
         } else {
@@ -500,6 +526,8 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const fnn_cuda_qweight *w = a.w;
     P8 p{};
     p.frag = w->frag;
+    p.frag_bs = w->frag_bs;
+    p.codebook = w->codebook;
     p.scales = w->scales;
     p.zeros = w->zeros;
     p.act = a.a;
@@ -514,65 +542,71 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     p.gather_on = a.gather != nullptr;
     if (a.gather) p.g = *a.gather;
     const int cols = 2 * p.M;   // int8 pairs
-    const int Kpad = p.KB * TT::KBLK;
-    const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * 512;
-    const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * (MULTI ? 8 : 2) + 16) * 4 + 64;
+    constexpr int MR = 4 * CG;
+    const size_t ring = (size_t)kG8 * kW8 * kS8 * kU8 * 2 * (512 + (TT::codebook ? 128 : 0));
+    const size_t fixed = ring + (size_t)(kG8 * 2 * kW8 * CG * 128 + kG8 * kW8 * MR * 2 + 3 * MR) * 4 + 64;
     const size_t per_tile = (size_t)kG8 * (CG * 512 + 192);
-    const size_t cap = 226 * 1024;
-    // one block per SM whenever the per-group accumulators of ceil(tiles / groups) tiles fit next to
-    // at least one ring chunk of activations; otherwise more blocks, run in waves
-    const size_t min_act = (size_t)cols * (TT::KBLK * kU8 + TT::PAD) + 16;
-    FNN_REQUIRE(fixed + per_tile + min_act <= cap, FNN_ERR_UNSUPPORTED,
+    frag::FragSizing sz;
+    const bool fits = frag::size_frag_launch(
+        ctx->sm_count, p.ntiles, kG8, p.KB * TT::KBLK, TT::KBLK, fixed, per_tile,
+        [&](int kc) {
+            return ((((size_t)cols * (kc + TT::PAD)) + 15) & ~(size_t)15) +
+                   (TT::codebook ? (size_t)(kc / 32) * 8 * CG * 4 : 0);
+        },
+        &sz);
+    FNN_REQUIRE(fits, FNN_ERR_UNSUPPORTED,
                 "qmatmul: shared memory budget exceeded for M=%d on the 8-bit fragment kernel", p.M);
-    int grid = ctx->sm_count;
-    int tpg = (int)div_ceil((size_t)p.ntiles, (size_t)grid * kG8);
-    const int tpg_max = (int)((cap - fixed - min_act) / per_tile);
-    if (tpg > tpg_max) {
-        tpg = tpg_max;
-        grid = (int)div_ceil((size_t)p.ntiles, (size_t)kG8 * tpg);
-    }
-    if (tpg < 1) tpg = 1;
-    grid = (int)std::min<size_t>((size_t)grid, div_ceil((size_t)p.ntiles, (size_t)kG8));
-    p.tiles_per_group = tpg;
-    const size_t act_budget = cap - fixed - (size_t)tpg * per_tile;
-    int Kc = Kpad;
-    while ((size_t)cols * (Kc + TT::PAD) + 16 > act_budget && Kc > TT::KBLK * kU8)
-        Kc = (Kc / 2 + TT::KBLK - 1) / TT::KBLK * TT::KBLK;
-    p.Kc = Kc;
-    const size_t act_bytes = (((size_t)cols * (Kc + TT::PAD)) + 15) & ~(size_t)15;
-    const size_t smem = act_bytes + fixed + (size_t)tpg * per_tile;
+    p.tiles_per_group = sz.tiles_per_group;
+    p.Kc = sz.Kc;
     auto kern = qmm_mma8_kernel<FMT, CG, kG8, MULTI>;
-    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sz.smem),
                    FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(kern, grid, kG8 * kW8 * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, sz.grid, kG8 * kW8 * 32, sz.smem, ctx->stream, p), FNN_ERR_DISPATCH);
     ctx->launches++;
-    ctx->last_path = "mma";
+    ctx->last_path = "mma8";
     return FNN_OK;
+}
+
+// Groups per block: three while that still gives (nearly) every SM a block; layers with fewer row
+// tiles run two or one group per block so that the tiles spread over more SMs.  Two and four column
+// groups (5..8 and 9..16 batch rows) keep more accumulators per thread and run at most two groups.
+template <int FMT, int CG>
+int launch8_cg(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
+    if (CG == 1) {
+        const bool multi = a.M > 1;
+        // (the codebook format keeps its two lookup tables in registers: two groups at most)
+        if constexpr (!T8<FMT>::codebook)
+            if ((ntiles + 2) / 3 >= want)
+                return multi ? launch8<FMT, 1, 3, true>(ctx, a) : launch8<FMT, 1, 3, false>(ctx, a);
+        if ((ntiles + 1) / 2 >= want)
+            return multi ? launch8<FMT, 1, 2, true>(ctx, a) : launch8<FMT, 1, 2, false>(ctx, a);
+        return multi ? launch8<FMT, 1, 1, true>(ctx, a) : launch8<FMT, 1, 1, false>(ctx, a);
+    }
+    if ((ntiles + 1) / 2 >= want) return launch8<FMT, CG, 2, true>(ctx, a);
+    return launch8<FMT, CG, 1, true>(ctx, a);
 }
 
 template <int FMT>
 int launch8_fmt(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const int M = (int)a.M;
-    FNN_REQUIRE(2 * M <= 8, FNN_ERR_UNSUPPORTED,
-                "qmatmul: the 8-bit fragment kernel holds one 8-column group of int8 pairs (M=%d)", M);
-    // Groups per block: three while that still gives (nearly) every SM a block; layers with fewer row
-    // tiles run two or one group per block so that the tiles spread over more SMs.
-    const int ntiles = (int)div_ceil(a.w->N, 16), want = ctx->sm_count * 4 / 5;
-    const bool multi = M > 1;
-    if ((ntiles + 2) / 3 >= want)
-        return multi ? launch8<FMT, 1, 3, true>(ctx, a) : launch8<FMT, 1, 3, false>(ctx, a);
-    if ((ntiles + 1) / 2 >= want)
-        return multi ? launch8<FMT, 1, 2, true>(ctx, a) : launch8<FMT, 1, 2, false>(ctx, a);
-    return multi ? launch8<FMT, 1, 1, true>(ctx, a) : launch8<FMT, 1, 1, false>(ctx, a);
+    FNN_REQUIRE(M >= 1 && M <= kMma8MaxRows, FNN_ERR_UNSUPPORTED,
+                "qmatmul: the 8-bit fragment kernel holds up to %d batch rows as int8 pairs (M=%d)",
+                kMma8MaxRows, M);
+    if (M <= 4) return launch8_cg<FMT, 1>(ctx, a);
+    if (M <= 8) return launch8_cg<FMT, 2>(ctx, a);
+    return launch8_cg<FMT, 4>(ctx, a);
 }
 
 }  // namespace
 
 bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M) {
-    // Measured on B200: s8 operands beat the fp16 fragment kernel up to four batch rows for every
-    // format whose values are small integers (I8, I4, and FP4 doubled); `mma.sync` with e4m3 operands
-    // runs at a fraction of the fp16 rate there, so FP8 stays on the fp16 kernel.
-    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4 || w->fmt == FNN_FMT_F4) && M >= 1 && M <= 4 &&
+    // Every format whose values are small integers (I8, I4, and FP4 doubled) runs on s8 operands with
+    // the activations as exact int8 pairs; `mma.sync` with e4m3 operands runs at a fraction of the
+    // fp16 rate on this part, so FP8 stays on the fp16 kernel.
+    return (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_I4 || w->fmt == FNN_FMT_F4 || w->fmt == FNN_FMT_I4CB) &&
+           M >= 1 &&
+           M <= (size_t)kMma8MaxRows &&
            w->N < (1u << 27) &&
            w->K < (1u << 27);
 }
@@ -615,6 +649,8 @@ int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         return launch8_fmt<FNN_FMT_I4>(ctx, a);
     case FNN_FMT_F4:
         return launch8_fmt<FNN_FMT_F4>(ctx, a);
+    case FNN_FMT_I4CB:
+        return launch8_fmt<FNN_FMT_I4CB>(ctx, a);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: the 8-bit fragment kernel does not cover format %d",
                      a.w->fmt);

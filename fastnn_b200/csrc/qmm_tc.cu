@@ -1,7 +1,8 @@
-// tcgen05 / TMEM / TMA kernel for the quantized MatMul with natively supported weight codes:
-// I8 through kind::i8, FP8-e4m3 through kind::f8f6f4.  No weight bit is touched by an ALU: TMA
-// drops the reference's own K-contiguous rows into 128-byte-swizzled shared memory and the
-// tensor core reads them from there.
+// tcgen05 / TMEM / TMA kernel for the quantized MatMul.  I8 runs through kind::i8 and FP8-e4m3 through
+// kind::f8f6f4 with no weight bit touched by an ALU: TMA drops the reference's own K-contiguous rows
+// into 128-byte-swizzled shared memory and the tensor core reads them from there.  I4 (as int8), FP4
+// (as the e4m3 code of the same value) and the codebook format (fp16 of block scale x centroid,
+// kind::f16) read a tile-major, pre-swizzled expansion of their codes.
 //
 // Orientation: the weight tile is the MMA's M operand (128 output channels per CTA) and the
 // batch is its N operand, so the same kernel serves one batch row and thousands:
@@ -518,8 +519,11 @@ int encode_weight_map(CUtensorMap *map, const fnn_cuda_qweight *w, int Kbytes) {
     return encode_map(map, (void *)w->rows, 2, dims, strides, box);
 }
 
+// Scratch of one call: the rewritten activations Bq[T][Mpad][Kp], then dq[Mpad] and rowsum[Mpad].
+// `fixed_scratch` null: the context's growable buffer; otherwise a caller-supplied region of
+// `fixed_bytes` that must already be large enough (the entry point that may not allocate).
 template <int KIND, int T>
-int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = nullptr, size_t fixed_bytes = 0) {
     const fnn_cuda_qweight *w = a.w;
     constexpr int ES = (KIND == KIND_F16) ? 2 : 1;  // bytes per operand element
     const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
@@ -531,12 +535,22 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     const int m_tiles = (M + Mb - 1) / Mb;
     const int Mpad = m_tiles * Mb;
 
-    // scratch: Bq[T][Mpad][Kp] | dq[Mpad] | rowsum[Mpad]
     const size_t bq_bytes = (size_t)T * Mpad * Kp;
     const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
-    int rc = ensure_scratch(ctx, bq_al + (size_t)Mpad * 8 + 256);
-    if (rc != FNN_OK) return rc;
-    uint8_t *bq = (uint8_t *)ctx->scratch;
+    const size_t need = bq_al + (size_t)Mpad * 8 + 256;
+    int rc = FNN_OK;
+    uint8_t *bq;
+    if (fixed_scratch) {
+        FNN_REQUIRE(need <= fixed_bytes, FNN_ERR_MEMORY,
+                    "qmatmul_noalloc: M=%d, K=%d needs %zu bytes of activation scratch; the built-in "
+                    "scratch holds %zu (use fnn_cuda_qmatmul for larger problems)",
+                    M, K, need, fixed_bytes);
+        bq = fixed_scratch;
+    } else {
+        rc = ensure_scratch(ctx, need);
+        if (rc != FNN_OK) return rc;
+        bq = (uint8_t *)ctx->scratch;
+    }
     float *dq = (float *)(bq + bq_al);
     float *rowsum = dq + Mpad;
     if (Mpad > M)  // padded batch rows of every term plane must read as zero
@@ -595,95 +609,9 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
                    FNN_ERR_DISPATCH);
     FNN_CUDA_CHECK(launch_pdl(kern, grid, kThreadsTc, smem, ctx->stream, map_w, map_a, p), FNN_ERR_DISPATCH);
     ctx->launches++;
-    ctx->last_path = "tc";
+    ctx->last_path = fixed_scratch ? "tc-noalloc" : "tc";
     return FNN_OK;
 }
-
-
-// Same launch sequence over caller-supplied scratch: used by the entry point that may not allocate.
-template <int KIND, int T>
-int launch_tc_static(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *scratch, size_t scratch_bytes) {
-    const fnn_cuda_qweight *w = a.w;
-    const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
-    const int Kp = (K + 15) & ~15;  // TMA strides are multiples of 16 bytes
-    // batch rows per tile: T*Mb is the MMA N (multiple of 16, at most 256)
-    const int mb_max = (T == 2) ? 128 : 80;
-    int Mb = std::min(mb_max, (M + 15) & ~15);
-    const int m_tiles = (M + Mb - 1) / Mb;
-    const int Mpad = m_tiles * Mb;
-
-    // scratch: Bq[T][Mpad][Kp] | dq[Mpad] | rowsum[Mpad]
-    const size_t bq_bytes = (size_t)T * Mpad * Kp;
-    const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
-    int rc = FNN_OK;
-    const size_t need = bq_al + (size_t)Mpad * 8 + 256;
-    FNN_REQUIRE(need <= scratch_bytes, FNN_ERR_MEMORY,
-                "qmatmul_noalloc: M=%d, K=%d needs %zu bytes of activation scratch; the built-in "
-                "scratch holds %zu (use fnn_cuda_qmatmul for larger problems)",
-                M, K, need, scratch_bytes);
-    uint8_t *bq = scratch;
-    float *dq = (float *)(bq + bq_al);
-    float *rowsum = dq + Mpad;
-    if (Mpad > M)  // padded batch rows of every term plane must read as zero
-        FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
-                                         (size_t)(Mpad - M) * Kp, T, ctx->stream),
-                       FNN_ERR_DISPATCH);
-    // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
-    // kernels makes every SM reconfigure (and drain) twice per call
-    FNN_CUDA_CHECK(cudaFuncSetAttribute(act_prep_kernel<KIND, T>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                        cudaSharedmemCarveoutMaxShared),
-                   FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
-                   FNN_ERR_DISPATCH);
-    ctx->launches++;
-
-    CUtensorMap map_w, map_a;
-    {
-        rc = encode_weight_map(&map_w, w, K);
-        if (rc != FNN_OK) return rc;
-    }
-    {
-        cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Mpad, (cuuint64_t)T};
-        cuuint64_t strides[2] = {(cuuint64_t)Kp, (cuuint64_t)Kp * Mpad};
-        cuuint32_t box[3] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)Mb, (cuuint32_t)T};
-        rc = encode_map(&map_a, bq, 3, dims, strides, box);
-        if (rc != FNN_OK) return rc;
-    }
-
-    TcParams p{};
-    p.scales = w->scales;
-    p.zeros = w->zeros;
-    p.bias = a.bias;
-    p.dq = dq;
-    p.rowsum = rowsum;
-    p.out = a.out;
-    p.err_flag = ctx->err_flag;
-    p.M = M;
-    p.N = N;
-    p.K = K;
-    p.Mb = Mb;
-    p.n_tiles = (N + kTileN - 1) / kTileN;
-    p.m_tiles = m_tiles;
-    p.kblocks = (K + kKBlockBytes - 1) / kKBlockBytes;
-    p.tiled = w->tc != nullptr;
-    p.w_tiles = (const unsigned char *)w->tc;
-    p.epilogue = a.epilogue;
-    const int a_bytes = kTileN * kKBlockBytes;
-    const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
-    int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride));
-    stages = std::max(2, std::min(stages, 8));
-    p.stages = stages;
-    const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride) + (2 * stages + 4) * 8 + 64;
-    const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
-    auto kern = qmm_tc_kernel<KIND, T>;
-    FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                   FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(kern, grid, kThreadsTc, smem, ctx->stream, map_w, map_a, p), FNN_ERR_DISPATCH);
-    ctx->launches++;
-    ctx->last_path = "tc-noalloc";
-    return FNN_OK;
-}
-
 
 // Position i of the tile-major copy -> (weight row n, byte offset inside the row's operand bytes).
 // Each 16 KB tile is stored the way the 128-byte swizzle lays it out in shared memory (16-byte chunk
@@ -745,7 +673,7 @@ bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
     // codes the tensor core takes natively (I8, FP8), after an exact one-byte expansion (I4, FP4),
     // or -- the codebook format, whose block scales vary inside K -- as an fp16 copy of
     // blockscale * centroid (only when those stay inside the fp16 range)
-    if (w->fmt == FNN_FMT_I4CB && !w->mma_ok) return false;
+    if (w->fmt == FNN_FMT_I4CB && !w->fp16_ok) return false;
     return w->K >= 128 && w->N >= 1 && w->N < (1u << 30) && w->K < (1u << 29);
 }
 
@@ -852,11 +780,11 @@ extern "C" int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, 
     switch (w->fmt) {
     case FNN_FMT_I8:
     case FNN_FMT_I4:
-        return launch_tc_static<KIND_I8, 2>(ctx, args, scratch, kNoAllocScratchBytes);
+        return launch_tc<KIND_I8, 2>(ctx, args, scratch, kNoAllocScratchBytes);
     case FNN_FMT_F8:
     case FNN_FMT_F4:
-        return M >= 128 ? launch_tc_static<KIND_F8, 2>(ctx, args, scratch, kNoAllocScratchBytes)
-                        : launch_tc_static<KIND_F8, 3>(ctx, args, scratch, kNoAllocScratchBytes);
+        return M >= 128 ? launch_tc<KIND_F8, 2>(ctx, args, scratch, kNoAllocScratchBytes)
+                        : launch_tc<KIND_F8, 3>(ctx, args, scratch, kNoAllocScratchBytes);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul_noalloc: format %d", w->fmt);
 }

@@ -137,14 +137,14 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
     bool any_zero = false;
     if (fmt == FNN_FMT_I4CB) {
         s_host.assign(scales, scales + n_scales);
-        // the tensor-core kernel folds the block scale in fp16: keep it to weights whose block
-        // scales and centroids are comfortably inside that range
+        // the tcgen05 kernel dequantizes to fp16 (block scale times centroid): keep it to weights
+        // whose block scales and centroids are comfortably inside that range
         for (size_t i = 0; i < n_scales; ++i) {
             float v = scales[i];
-            if (!(v == 0.0f || (v >= 1e-4f && v <= 3e4f))) w->mma_ok = false;
+            if (!(v == 0.0f || (v >= 1e-4f && v <= 3e4f))) w->fp16_ok = false;
         }
         for (int i = 0; i < 16; ++i)
-            if (!(codebook16[i] >= -4.0f && codebook16[i] <= 4.0f)) w->mma_ok = false;
+            if (!(codebook16[i] >= -4.0f && codebook16[i] <= 4.0f)) w->fp16_ok = false;
     } else {
         s_host.resize(N);
         z_host.resize(N);

@@ -75,9 +75,13 @@ typedef struct fnn_cuda_graph fnn_cuda_graph;
  * One per executor.  All work of a context is asynchronous on one CUDA stream;
  * calls are serialized by the caller, as `CpuBackend::dispatch` is single-threaded
  * by contract (src/backend/cpu/mod.rs:176-187). */
-int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out);
-/* Same, but runs on a stream the caller owns (a `cudaStream_t` passed as void*). */
+int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out);   /* on a private non-blocking stream */
+/* Same, but runs on the stream the caller gives (a `cudaStream_t` passed as void*) and never on
+ * another one: a null handle is the legacy default stream (on which stream capture, and so
+ * fnn_cuda_graph_begin, is not possible). */
 int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out);
+/* The `cudaStream_t` the context launches on (so that a caller can order its own work against it). */
+void *fnn_cuda_ctx_stream(fnn_cuda_ctx *ctx);
 int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx);
 int fnn_cuda_sync(fnn_cuda_ctx *ctx);
 /* Message of the last failing call on this thread ("" if none). */
@@ -161,7 +165,9 @@ int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_
  * of device memory to an allocator of their own, or run a latency-critical loop in which
  * cudaMalloc/cudaFree (which can synchronize the whole device) are off limits; fnn_cuda_qmatmul
  * may grow the context's scratch buffer on a larger problem, this entry point never calls
- * cudaMalloc, cudaFree or any allocating routine.  It runs the tcgen05 kernel with the rewritten
+ * cudaMalloc, cudaFree or any allocating routine; after the first call per device (which makes the
+ * CUDA runtime load the module and materialise the array) free device memory does not change
+ * across a call.  It runs the tcgen05 kernel with the rewritten
  * activations placed in an 8 MiB scratch array that is part of the library image (every GPU
  * that loads the library holds it until the process exits).  The rewritten activations must
  * fit in it: about T * M * K bytes with M and K rounded up to the kernel's tiles (T = 2 byte
@@ -244,7 +250,10 @@ int fnn_cuda_fill(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t offset, size_
 /* ---- replay and timing --------------------------------------------------------------
  * A static-shape plan is replayed unchanged after its first execution
  * (src/backend/executor.rs:639-667); capture it once and relaunch it as a CUDA graph.
- * Between begin and end every call on `ctx` is recorded instead of executed. */
+ * Between begin and end every call on `ctx` is recorded instead of executed.  A graph keeps the
+ * addresses it was captured with: the context's scratch buffer is never freed while the context
+ * lives (when a later, larger call outgrows it the old one is retired, not released), so a graph
+ * stays valid whatever runs on the context afterwards. */
 int fnn_cuda_graph_begin(fnn_cuda_ctx *ctx);
 int fnn_cuda_graph_end(fnn_cuda_ctx *ctx, fnn_cuda_graph **out);
 int fnn_cuda_graph_launch(fnn_cuda_ctx *ctx, fnn_cuda_graph *g);

@@ -176,6 +176,21 @@ def test_symbolic_batch_resolves_from_input_bytes():
         GraphExecutor.shape_env_from_inputs(g, [bytes(5 * 64 * 4 + 4)])
 
 
+@pytest.mark.parametrize("shape,rows", [(["d1", 8, 64], 40), ([4, "d1", 64], 20), ([3, 2, 64], 6)])
+def test_batch_rows_are_the_product_of_all_leading_dims(shape, rows):
+    """A symbolic leading dimension next to other leading dimensions: M = their product."""
+    gb = GraphBuilder()
+    x = gb.input_with_dims(shape)
+    w = gb.constant(normal(1, (64, 16), 0.02), TensorType.new([64, 16]))
+    y = gb.matmul(x, w)
+    g = gb.to_graph()
+    g.inputs, g.outputs = gb.recorded_input_ids(), [y.node_id()]
+    plan, mp, cg = compile_graph(g, WeightDtype.I8)
+    call = [i for i in plan.instructions if isinstance(i, fnn.CallKernel)][0]
+    env = fnn.ShapeEnv({"d1": 5})
+    assert fnn.backend.resolve_params(call.params, call.param_dims, env, 3) == [rows, 64, 16]
+
+
 def test_quantize_argument_validation():
     assert WeightDtype.from_quantize(4) == WeightDtype.I4
     assert WeightDtype.from_quantize("i4cb") == WeightDtype.I4Codebook

@@ -59,7 +59,7 @@ def test_config1_linear_i4_bias_through_graph_builder(backend):
     out = gb.compile_and_execute_with_quantize([y], backend, [x.tobytes()], 4)
     got = np.frombuffer(out[0], np.float32).reshape(m, n)
     want = orc.qmatmul(orc.quantize_kn(orc.FMT_I4, w), x, b, orc.EPI_NONE)
-    assert max_err_vs_rms(got, want) <= 1e-2
+    assert max_err_vs_rms(got, want) <= 1e-3
     # the quantized result is also close to the f32 layer (tests/quantized_pipeline.rs bounds)
     ref = x @ w + b
     assert np.sqrt(np.mean((got - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)) < 0.2
@@ -81,7 +81,7 @@ def test_compile_with_weight_dtype_fp_formats(backend, wd):
     want = orc.qmatmul(orc.quantize_kn(fmt, w), x, None, orc.EPI_SILU)
     for _ in range(2):  # second call replays the static plan without WriteConst
         got = np.frombuffer(ex.execute(cg, plan, mp, [x.tobytes()])[0], np.float32).reshape(m, n)
-        assert max_err_vs_rms(got, want) <= 1e-2
+        assert max_err_vs_rms(got, want) <= 1e-3
     prof = ex.execute_profile(cg, plan, mp, [x.tobytes()])
     assert [p.kernel_name for p in prof][-1].startswith("matmul_") and prof[-1].elapsed_ns > 0
 
@@ -113,7 +113,7 @@ def test_aot_executor_i4cb_mlp_stack_with_residual(backend):
         up = orc.qmatmul(orc.quantize_kn(orc.FMT_I4CB, params[f"w_up{i}"]), ref, params[f"b_up{i}"], orc.EPI_GELU)
         dn = orc.qmatmul(orc.quantize_kn(orc.FMT_I4CB, params[f"w_dn{i}"]), up, params[f"b_dn{i}"], orc.EPI_NONE)
         ref = dn + ref
-    assert max_err_vs_rms(got, ref) <= 1e-2
+    assert max_err_vs_rms(got, ref) <= 1e-3
     assert aot.memory_stats()["arena_bytes"] > 0
 
 
@@ -126,7 +126,7 @@ def test_symbolic_batch_dimension(backend):
     for m in (1, 5, 3):
         x = normal(60 + m, (m, k), 1.0)
         got = aot.forward({"x": x})["y"]
-        assert got.shape == (m, n) and max_err_vs_rms(got, orc.qmatmul(q, x)) <= 1e-2
+        assert got.shape == (m, n) and max_err_vs_rms(got, orc.qmatmul(q, x)) <= 1e-3
 
 
 def test_unsupported_paths_fail_loudly(backend):

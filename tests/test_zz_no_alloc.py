@@ -5,8 +5,12 @@ cudaMalloc-induced device synchronization is not acceptable).
 The entry point keeps its activation scratch in an array inside the library image instead of
 growing the context's scratch buffer.  Checked here through the C ABI against the regular
 entry point on the same inputs, on two calls in a row: the second call is smaller than the
-first, so it only passes if stale scratch contents from the first call are handled.  This file
-is collected last on purpose; it also passes when run alone in a fresh process.
+first, so it only passes if stale scratch contents from the first call are handled.  A second test
+checks the property the entry point is named for: free device memory does not move across a call,
+and the context's own scratch buffer is still empty afterwards.
+
+The file name sorts last so that a run that stops at the first failure (-x) has already run
+every other test when it gets here; the tests also pass when run alone in a fresh process.
 """
 import ctypes
 
@@ -66,6 +70,42 @@ def test_noalloc_entry_matches_regular_entry_on_two_calls(backend, fmt):
     finally:
         w.close()
         arena.close()
+
+
+def test_noalloc_entry_leaves_device_memory_and_context_scratch_untouched():
+    """On a fresh context (no scratch yet): after the first call per device (which loads the
+    module and looks up the array's address) a call moves cudaMemGetInfo's free bytes by nothing,
+    and a regular tcgen05 call of the same size inside a capture still reports that the context's
+    scratch would have to grow -- so the entry point did not grow it behind the caller's back."""
+    import torch
+    fresh = fnn.CudaBackend(0)
+    lib = fresh.lib
+    k, n, m = 1024, 256, 64
+    q = orc.quantize_kn(orc.FMT_I8, normal(930, (k, n), 0.02))
+    arena, w, (a_off, out_off, _, _) = _device_rig(fresh, q, m)
+    base = arena.device_ptr
+    try:
+        fresh.write_arena(arena, a_off, normal(931, (m, k), 1.0).tobytes())
+        call = lambda: lib.fnn_cuda_qmatmul_noalloc(fresh.ctx, w.handle, base + a_off, base + out_off,
+                                                    None, m, L.EPI_NONE)
+        assert call() == 0, L.last_error()          # first call on the device: set-up happens here
+        fresh.synchronize()
+        free_before = torch.cuda.mem_get_info(0)[0]
+        assert call() == 0, L.last_error()
+        fresh.synchronize()
+        assert torch.cuda.mem_get_info(0)[0] == free_before
+        assert lib.fnn_cuda_graph_begin(fresh.ctx) == 0
+        rc = lib.fnn_cuda_qmatmul_ptr(fresh.ctx, w.handle, base + a_off, base + out_off, None, m,
+                                      L.EPI_NONE, L.PATH_TC)
+        msg = L.last_error()
+        g = ctypes.c_void_p()
+        assert lib.fnn_cuda_graph_end(fresh.ctx, ctypes.byref(g)) == 0
+        lib.fnn_cuda_graph_free(g)
+        assert rc == 3 and "scratch buffer must grow" in msg
+    finally:
+        w.close()
+        arena.close()
+        fresh.close()
 
 
 def test_noalloc_entry_refuses_what_does_not_fit_or_would_allocate(backend):
