@@ -202,20 +202,16 @@ class Layer:
         err = np.max(np.abs(got[np.ix_(ms, rows)] - want)) / max(np.sqrt(np.mean(want ** 2)), 1e-30)
         return float(err)
 
-    def time_isolated(self, epi, path=0, reps=20):
-        """Median CUDA-event time of single launches, each alone on the stream (synchronize and an L2
-        flush before it: no neighbouring kernel to overlap with, weights cold)."""
-        b, lib = self.backend, self.backend.lib
-        times, ms = [], ctypes.c_float()
-        for i in range(reps):
-            check(lib.fnn_cuda_flush_l2(b.ctx), self.fnn)
-            b.synchronize()
-            check(lib.fnn_cuda_timer_start(b.ctx, 1), self.fnn)
-            self.launch(i, epi, path)
-            check(lib.fnn_cuda_timer_stop(b.ctx, 1), self.fnn)
-            check(lib.fnn_cuda_timer_elapsed_ms(b.ctx, 1, ctypes.byref(ms)), self.fnn)
-            times.append(float(ms.value))
-        return float(np.median(times))
+    def time_isolated(self, steps, epi, path=0):
+        """Per-launch time with programmatic dependent launch off: the same graph replay over the
+        rotating weight replicas, but every kernel starts only after the one before it has
+        finished, so no launch overlaps its neighbour's tail.  Returns ms per launch."""
+        lib, b = self.backend.lib, self.backend
+        check(lib.fnn_cuda_ctx_set_overlap(b.ctx, 0), self.fnn)
+        try:
+            return self.time_steps(steps, 3, epi, path) / steps
+        finally:
+            check(lib.fnn_cuda_ctx_set_overlap(b.ctx, 1), self.fnn)
 
     def time_steps(self, steps, warmup, epi, path=0, min_seconds=0.0):
         """CUDA-event time of `steps` launches replayed from one captured graph."""
@@ -344,7 +340,7 @@ def run_sweep(fnn, backend, peaks, budget_s=420.0, only=None, only_m=None, steps
                 steps = steps_override or int(min(200, max(5, 0.05 / est)))
                 ms_total = layer.time_steps(steps, 3, epi, path)
                 t = ms_total / steps * 1e-3
-                iso = layer.time_isolated(epi, path, reps=10 if est < 1e-4 else 3)
+                iso = layer.time_isolated(steps, epi, path)
                 gbs, tfs = layer.alg_bytes / t / 1e9, layer.flops / t / 1e12
                 out.append({"point": label, "m": m, "k": k, "n": n, "path": backend.last_path(),
                             "us": round(t * 1e6, 2), "isolated_us": round(iso * 1e3, 2),
@@ -434,7 +430,7 @@ def run_ours(args):
             "clocks": clocks, "gpu_launches": launches,
         }
     if world == 1:
-        iso_ms = layer.time_isolated(L.EPI_SILU)
+        iso_ms = layer.time_isolated(min(args.steps, 500), L.EPI_SILU)
         line["isolated_us"] = round(iso_ms * 1e3, 2)
         line["roofline"]["isolated_frac"] = round(layer.alg_bytes / (iso_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         line["roofline"]["note"] = ("achieved/frac: back-to-back replay of one CUDA graph (the next launch's "

@@ -27,6 +27,7 @@ SIGNATURES = {
     "fnn_cuda_ctx_create": (_int, [_int, _c.POINTER(_vp)]),
     "fnn_cuda_ctx_create_on_stream": (_int, [_int, _vp, _c.POINTER(_vp)]),
     "fnn_cuda_ctx_stream": (_vp, [_vp]),
+    "fnn_cuda_ctx_set_overlap": (_int, [_vp, _int]),
     "fnn_cuda_ctx_destroy": (_int, [_vp]),
     "fnn_cuda_sync": (_int, [_vp]),
     "fnn_cuda_last_error": (_c.c_char_p, []),

@@ -154,6 +154,12 @@ int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out) 
 
 void *fnn_cuda_ctx_stream(fnn_cuda_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
+int fnn_cuda_ctx_set_overlap(fnn_cuda_ctx *ctx, int enabled) {
+    FNN_REQUIRE(ctx, FNN_ERR_DISPATCH, "ctx_set_overlap: null context");
+    ctx->overlap_launches = enabled != 0;
+    return FNN_OK;
+}
+
 int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx) {
     if (!ctx) return FNN_OK;
     cudaSetDevice(ctx->device);
@@ -498,7 +504,7 @@ int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_
     const float *a = (const float *)(arena->base + a_offset);
     const float *b = binary ? (const float *)(arena->base + b_offset) : a;
     float *o = (float *)(arena->base + out_offset);
-    FNN_CUDA_CHECK(launch_pdl(elementwise_kernel, grid_for(ctx, out_len, 256), 256, 0, ctx->stream, op, a,
+    FNN_CUDA_CHECK(launch_pdl(elementwise_kernel, grid_for(ctx, out_len, 256), 256, 0, ctx, op, a,
                               a_len, b, binary ? b_len : (size_t)1, o, out_len),
                    FNN_ERR_DISPATCH);
     ctx->launches++;

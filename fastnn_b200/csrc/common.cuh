@@ -65,6 +65,7 @@ struct fnn_cuda_ctx {
     size_t scratch_bytes = 0;
     std::vector<void *> retired_scratch;   // outgrown scratch buffers (captured graphs may still name them)
     int *err_flag = nullptr;  // device flag written by bounded waits that gave up
+    bool overlap_launches = true;   // programmatic dependent launch (fnn_cuda_ctx_set_overlap)
 };
 
 struct fnn_cuda_arena {
@@ -93,14 +94,6 @@ struct fnn_cuda_qweight {
     float *frag_bs = nullptr;   // I4CB block scales in fragment order
     bool fp16_ok = true;         // codebook format: false when block scales or centroids would leave the fp16 range
                                 // of the tcgen05 kernel's dequantized operand
-    // tile-major operand copy for the tcgen05 kernel (built on demand): [row tile of 128][K block of
-    // 128 bytes][128 rows][128 bytes], zero padded, so that every TMA box is 16 KB of contiguous memory.
-    // Only for the formats that need an expansion: one byte per weight (I4 -> int8, FP4 -> e4m3) or
-    // fp16 (codebook format); 8-bit codes are read in place from `rows`.
-    void *tc = nullptr;
-    size_t tc_bytes = 0;
-    size_t tc_kblocks = 0;      // K blocks per row tile
-    int tc_kind = 0;
 };
 
 struct fnn_cuda_graph {
@@ -213,18 +206,18 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem, const fnn_cuda_ctx *ctx,
                               Args &&...args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)block);
     cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
+    cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->overlap_launches ? 1 : 0;   // without it every kernel waits for the one before it
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 #endif

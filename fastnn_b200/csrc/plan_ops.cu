@@ -144,9 +144,9 @@ int fnn_cuda_row_norm(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, int kind, size_t
     FNN_REQUIRE(rows <= 0x7FFFFFFFu, FNN_ERR_DISPATCH, "row_norm: too many rows (%zu)", rows);
     const float *in = (const float *)(arena->base + in_offset);
     float *out = (float *)(arena->base + out_offset);
-    cudaError_t e = kind == 0 ? launch_pdl(row_norm_kernel<0>, (int)rows, kRowThreads, 0, ctx->stream, in, res, w,
+    cudaError_t e = kind == 0 ? launch_pdl(row_norm_kernel<0>, (int)rows, kRowThreads, 0, ctx, in, res, w,
                                            wn, b, bn, row_size, eps, out)
-                              : launch_pdl(row_norm_kernel<1>, (int)rows, kRowThreads, 0, ctx->stream, in, res, w,
+                              : launch_pdl(row_norm_kernel<1>, (int)rows, kRowThreads, 0, ctx, in, res, w,
                                            wn, b, bn, row_size, eps, out);
     FNN_CUDA_CHECK(e, FNN_ERR_DISPATCH);
     ctx->launches++;
@@ -173,7 +173,7 @@ int fnn_cuda_softmax(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t in_offset,
                 FNN_ERR_DISPATCH, "softmax: slice outside arena or misaligned");
     const size_t rows = len / axis_dim;
     FNN_REQUIRE(rows <= 0x7FFFFFFFu, FNN_ERR_DISPATCH, "softmax: too many rows (%zu)", rows);
-    FNN_CUDA_CHECK(launch_pdl(softmax_kernel, (int)rows, kRowThreads, 0, ctx->stream,
+    FNN_CUDA_CHECK(launch_pdl(softmax_kernel, (int)rows, kRowThreads, 0, ctx,
                               (const float *)(arena->base + in_offset), axis_dim, stride,
                               (float *)(arena->base + out_offset)),
                    FNN_ERR_DISPATCH);

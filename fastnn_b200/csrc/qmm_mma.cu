@@ -585,7 +585,7 @@ int launch_mma_g(fnn_cuda_ctx *ctx, const QmmArgs &a, const float *act, float *o
     auto kern = qmm_mma_kernel<FMT, CG, G>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(kern, grid, G * kW * 32, smem, ctx->stream, p), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, G * kW * 32, smem, ctx, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     return FNN_OK;
 }

@@ -561,7 +561,7 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     auto kern = qmm_mma8_kernel<FMT, CG, kG8, MULTI>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sz.smem),
                    FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(kern, sz.grid, kG8 * kW8 * 32, sz.smem, ctx->stream, p), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, sz.grid, kG8 * kW8 * 32, sz.smem, ctx, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     ctx->last_path = "mma8";
     return FNN_OK;

@@ -1,24 +1,32 @@
-// tcgen05 / TMEM / TMA kernel for the quantized MatMul.  I8 runs through kind::i8 and FP8-e4m3 through
-// kind::f8f6f4 with no weight bit touched by an ALU: TMA drops the reference's own K-contiguous rows
-// into 128-byte-swizzled shared memory and the tensor core reads them from there.  I4 (as int8), FP4
-// (as the e4m3 code of the same value) and the codebook format (fp16 of block scale x centroid,
-// kind::f16) read a tile-major, pre-swizzled expansion of their codes.
+// tcgen05 / TMEM / TMA kernel for the quantized MatMul.
 //
-// Orientation: the weight tile is the MMA's M operand (128 output channels per CTA) and the
-// batch is its N operand, so the same kernel serves one batch row and thousands:
+// Weight operand (the MMA's M side, 128 output channels per CTA tile), always fetched from the
+// packed rows as the reference stores them -- no expanded copy exists in device memory:
+//   I8    kind::i8, FP8 kind::f8f6f4 (e4m3): TMA drops the K-contiguous rows into 128-byte-swizzled
+//         shared memory and the tensor core reads them; no ALU touches a weight bit
+//   FP4   kind::f8f6f4 with an e2m1 A operand: the 4-bit tensor-map type unpacks sixteen packed
+//         codes (8 bytes) into each 16-byte slot of the swizzled tile; again no ALU
+//   I4    TMA brings the packed nibbles (64 bytes per row and K block); transform warps widen them
+//         in shared memory to int8 holding 16*q (two logic operations per eight weights) for
+//         kind::i8
+//   I4CB  TMA brings the nibbles and the block scales; transform warps write fp16 of
+//         block scale x centroid (one rounding) for kind::f16
+//
+// Orientation: the weight tile is the MMA's M operand and the batch is its N operand, so the same
+// kernel serves one batch row and thousands:
 //     D[n, (t,m)] += W[n, k] * Aq_t[m, k]          (accumulators in TMEM, 128 lanes = n)
 // f32 activations are first rewritten by `act_prep_kernel` as T narrow terms per element
 //   int8:  a ~= dq[m] * (128*hi + lo)             (15-bit fixed point per row, T = 2)
 //   e4m3:  a ~= dq[m] * (t1 + t2 + t3)            (three 4-bit-significand terms, T = 3)
-// which keeps the result within ~3e-4 of the f32-accumulated reference.  The epilogue reads the
-// accumulators with tcgen05.ld, recombines the terms and applies
+//   fp16:  one term (codebook format)
+// The epilogue reads the accumulators with tcgen05.ld, recombines the terms and applies
 //     out[m,n] = act(dq[m]*scale[n]*acc + zero[n]*sum_k a[m,k] + bias[n])
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
 //
-// Warp roles (320 threads): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
-// warps 2-9 = epilogue (a TMEM lane quadrant each, two warps per quadrant).  Every mbarrier wait is bounded: a wait
-// that runs out raises the context's error flag, every role leaves its loop, TMEM is freed and
-// the kernel returns.
+// Warp roles: warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer, warps 2-9 = epilogue (a TMEM
+// lane quadrant each, two warps per quadrant), warps 10-17 = transform (I4 / I4CB only).  Every
+// mbarrier wait is bounded: a wait that runs out raises the context's error flag, every role leaves
+// its loop, TMEM is freed and the kernel returns.
 #include "common.cuh"
 
 #include <algorithm>
@@ -32,10 +40,14 @@ namespace {
 constexpr int kTileN = 128;        // weight rows (output channels) per CTA tile = MMA M
 constexpr int kKBlockBytes = 128;  // bytes of K per pipeline stage = one 128B swizzle row
 constexpr int kEpiWarps = 8;                      // two per TMEM lane quadrant
-constexpr int kThreadsTc = (2 + kEpiWarps) * 32;
+constexpr int kXfWarps = 8;                       // transform warps (formats widened in shared memory)
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: far beyond any legitimate wait
 
 enum { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };
+// How the weight tile reaches the MMA: straight from TMA (I8, FP8, FP4), or through the transform
+// warps (I4 -> int8, codebook -> fp16).
+enum { WF_TMA = 0, WF_I4 = 1, WF_CB = 2 };
+constexpr int kFmtE4M3 = 0, kFmtE2M1 = 5;        // operand format codes of kind::f8f6f4
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 
@@ -85,13 +97,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-// Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
@@ -155,17 +160,22 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor: D format, A/B formats, K-major both, N (>>3) and M (>>4).
-__host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols) {
+// Instruction descriptor: D format, A/B formats, K-major both, N (>>3) and M (>>4).  `a_fmt`: the
+// A operand's format code for kind::f8f6f4 (e4m3 or e2m1); B is e4m3 there.  Format 0 is F16 for
+// kind::f16.
+__host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols, int a_fmt) {
     return (kind == KIND_I8 ? (2u << 4) | (1u << 7) | (1u << 10)   // S32 accum, signed 8-bit A and B
-                            : (1u << 4) | (0u << 7) | (0u << 10))  // F32 accum; format 0 = E4M3 (f8f6f4) or F16 (f16)
+                            : (1u << 4) | ((uint32_t)a_fmt << 7) | (0u << 10))  // F32 accum
            | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
 }
+// generic-proxy writes to shared memory -> visible to the async proxy (the tensor core's reads)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- activation rewrite ---------------------------------------------------------------------
 // One block per batch row.  Writes T byte planes Bq[t][m][Kp] (rows zero-padded to Kp), the
-// per-row factor dq[m] and the row sum.
-template <int KIND, int T>
+// per-row factor dq[m] and the row sum.  PERM8: inside every group of eight k the bytes are stored
+// in the order 0,2,4,6,1,3,5,7 -- the order in which the I4 transform emits its weights.
+template <int KIND, int T, bool PERM8>
 __global__ void __launch_bounds__(256)
 act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
                 float *__restrict__ dq, float *__restrict__ rowsum) {
@@ -198,17 +208,22 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
         mx = fmaxf(mx, s_max[w]);
         sum += s_sum[w];
     }
-    const float full = (KIND == KIND_I8) ? 16256.0f : 448.0f;
     if (KIND == KIND_F16) {
-        // one fp16 term, no rescaling: bq is [Mpad][Kp bytes] of halves
+        // one fp16 term; the row is scaled by a power of two so that its largest element sits just
+        // below 2^15 (exact, any f32 magnitude fits): bq is [Mpad][Kp bytes] of halves
+        int ex = 15;
+        if (mx > 0.0f && isfinite(mx)) (void)frexpf(mx, &ex);
+        const int e = max(-120, min(120, 15 - ex));
+        const float up = ldexpf(1.0f, e);
         if (tid == 0) {
-            dq[m] = 1.0f;
+            dq[m] = ldexpf(1.0f, -e);
             rowsum[m] = sum;
         }
         __half *dst = reinterpret_cast<__half *>(bq + (size_t)m * Kp);
-        for (int k = tid; k < Kp / 2; k += 256) dst[k] = __float2half_rn(k < K ? row[k] : 0.0f);
+        for (int k = tid; k < Kp / 2; k += 256) dst[k] = __float2half_rn(k < K ? row[k] * up : 0.0f);
         return;
     }
+    const float full = (KIND == KIND_I8) ? 16256.0f : 448.0f;
     const float step = (mx > 0.0f && isfinite(mx)) ? mx / full : 1.0f;
     const float inv = 1.0f / step;
     if (tid == 0) {
@@ -234,8 +249,10 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
                 r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
             }
         }
+        const int i8 = k & 7;
+        const int kk = PERM8 ? ((k & ~7) | ((i8 >> 1) + (i8 & 1) * 4)) : k;
 #pragma unroll
-        for (int i = 0; i < T; ++i) bq[((size_t)i * Mpad + m) * Kp + k] = t[i];
+        for (int i = 0; i < T; ++i) bq[((size_t)i * Mpad + m) * Kp + kk] = t[i];
     }
 }
 
@@ -247,37 +264,48 @@ struct TcParams {
     const float *bias;
     const float *dq;
     const float *rowsum;
+    const float *codebook;   // WF_CB: 16 centroids
     float *out;
     int *err_flag;
     int M, N, K;
     int Mb;        // batch rows per tile
     int n_tiles, m_tiles;
-    int kblocks;   // ceil(K / 128)
-    int tiled;     // weights come from the tile-major copy (one contiguous, pre-swizzled 16 KB per stage)
-    const unsigned char *w_tiles;
+    int kblocks;   // pipeline stages' worth of K: ceil(operand bytes per row / (128 * atoms))
+    int a_fmt;     // A operand format of kind::f8f6f4
+    float acc_scale;   // 1/16 when the int8 operand carries 16*q (I4)
     int stages;
     int epilogue;
 };
 
-template <int KIND, int T>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+// ATOMS: 128-byte swizzle atoms of K per pipeline stage (2 for fp16 operands: a stage is 128 k for
+// every format).  Shared memory per stage: operand tile, raw tile (transformed formats), activations.
+template <int KIND, int T, int WF>
+__global__ void __launch_bounds__((2 + kEpiWarps + (WF == WF_TMA ? 0 : kXfWarps)) * 32, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-              TcParams p) {
+              const __grid_constant__ CUtensorMap map_s, TcParams p) {
+    constexpr int ATOMS = (KIND == KIND_F16) ? 2 : 1;
+    constexpr int kRawBytes = (WF == WF_TMA) ? 0 : kTileN * 64;        // packed nibbles: 64 bytes per row
+    constexpr int kScBytes = (WF == WF_CB) ? kTileN * 16 : 0;          // four block scales per row
+    constexpr int kXf0 = 2 + kEpiWarps;                                // first transform warp
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is what the 128B swizzle atoms need
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int BNt = T * p.Mb;                       // MMA N: (term, batch row) columns
-    const int a_bytes = kTileN * kKBlockBytes;      // 16 KB weight tile per stage
-    const int b_bytes = BNt * kKBlockBytes;         // activation tile per stage
-    const int b_stride = (b_bytes + 1023) & ~1023;
+    const int BNt = T * p.Mb;                               // MMA N: (term, batch row) columns
+    const int a_atom = kTileN * kKBlockBytes;               // 16 KB operand atom
+    const int a_bytes = ATOMS * a_atom;
+    const int b_bytes = BNt * kKBlockBytes;                 // activation atom
+    const int b_atom = (b_bytes + 1023) & ~1023;
+    const int b_stride = ATOMS * b_atom;
     unsigned char *s_a = smem;
-    unsigned char *s_b = smem + (size_t)p.stages * a_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(s_b + (size_t)p.stages * b_stride);
-    uint64_t *full = bars, *empty = bars + p.stages;
-    uint64_t *tfull = bars + 2 * p.stages, *tempty = tfull + 2;
+    unsigned char *s_b = s_a + (size_t)p.stages * a_bytes;
+    unsigned char *s_raw = s_b + (size_t)p.stages * b_stride;             // [stages][raw | scales]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_raw + (size_t)p.stages * (kRawBytes + kScBytes));
+    uint64_t *full = bars, *empty = bars + p.stages, *rawfull = bars + 2 * p.stages;
+    uint64_t *tfull = bars + 3 * p.stages, *tempty = tfull + 2;
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(tempty + 2);
     volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+    float *s_cb = reinterpret_cast<float *>(s_tmem + 2);                  // [16]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();   // barrier set-up and the TMEM allocation below run under the previous kernel's tail
@@ -287,8 +315,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
+            // the MMA issuer waits for the activation tile (one arrival with a byte count) and, for the
+            // formats widened in shared memory, for every transform warp
+            mbar_init(&full[s], 1 + (WF == WF_TMA ? 0 : kXfWarps));
             mbar_init(&empty[s], 1);
+            mbar_init(&rawfull[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&tfull[i], 1);
@@ -297,6 +328,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (WF == WF_CB && threadIdx.x >= 32 && threadIdx.x < 48) s_cb[threadIdx.x - 32] = p.codebook[threadIdx.x - 32];
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(s_tmem)),
@@ -316,13 +348,28 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            auto load_a = [&](int st, int nt, int kb) {
-                if (p.tiled)
-                    bulk_load(s_a + (size_t)st * a_bytes, p.w_tiles + (size_t)(nt * p.kblocks + kb) * a_bytes,
-                              a_bytes, &full[st]);
-                else
-                    tma_load_2d(s_a + (size_t)st * a_bytes, &map_w, &full[st], kb * kKBlockBytes, nt * kTileN);
+            // weights of stage `st`: the operand tile itself, or the packed nibbles (+ block scales)
+            // for the transform warps
+            auto load_w = [&](int st, int nt, int kb) {
+                if (WF == WF_TMA) {
+#pragma unroll
+                    for (int at = 0; at < ATOMS; ++at)
+                        tma_load_2d(s_a + (size_t)st * a_bytes + at * a_atom, &map_w, &full[st],
+                                    (kb * ATOMS + at) * kKBlockBytes, nt * kTileN);
+                } else {
+                    unsigned char *raw = s_raw + (size_t)st * (kRawBytes + kScBytes);
+                    mbar_expect_tx(&rawfull[st], (uint32_t)(kRawBytes + kScBytes));
+                    tma_load_2d(raw, &map_w, &rawfull[st], kb * 64, nt * kTileN);
+                    if (WF == WF_CB) tma_load_2d(raw + kRawBytes, &map_s, &rawfull[st], kb * 16, nt * kTileN);
+                }
             };
+            auto load_b = [&](int st, int mt, int kb) {
+#pragma unroll
+                for (int at = 0; at < ATOMS; ++at)
+                    tma_load_3d(s_b + (size_t)st * b_stride + at * b_atom, &map_a, &full[st],
+                                (kb * ATOMS + at) * kKBlockBytes, mt * p.Mb, 0);
+            };
+            const uint32_t full_tx = (uint32_t)((WF == WF_TMA ? a_bytes : 0) + ATOMS * b_bytes);
             // The weights do not depend on the kernel before this one on the stream, the activation
             // planes do: the first ring of weight tiles is requested before griddepcontrol.wait, the
             // matching activation tiles after it.
@@ -330,12 +377,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             if (head > 0) {
                 const int nt = blockIdx.x / p.m_tiles, mt = blockIdx.x - nt * p.m_tiles;
                 for (int kb = 0; kb < head; ++kb) {
-                    mbar_expect_tx(&full[kb], (uint32_t)(a_bytes + b_bytes));   // stage kb: all stages start empty
-                    load_a(kb, nt, kb);
+                    mbar_expect_tx(&full[kb], full_tx);   // stage kb: all stages start empty
+                    load_w(kb, nt, kb);
                 }
                 pdl_wait();
-                for (int kb = 0; kb < head; ++kb)
-                    tma_load_3d(s_b + (size_t)kb * b_stride, &map_a, &full[kb], kb * kKBlockBytes, mt * p.Mb, 0);
+                for (int kb = 0; kb < head; ++kb) load_b(kb, mt, kb);
                 s = head;
                 if (s == p.stages) {
                     s = 0;
@@ -351,9 +397,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full[s], (uint32_t)(a_bytes + b_bytes));
-                    load_a(s, nt, kb);
-                    tma_load_3d(s_b + (size_t)s * b_stride, &map_a, &full[s], kb * kKBlockBytes, mt * p.Mb, 0);
+                    mbar_expect_tx(&full[s], full_tx);
+                    load_w(s, nt, kb);
+                    load_b(s, mt, kb);
                     if (++s == p.stages) {
                         s = 0;
                         phase ^= 1;
@@ -367,7 +413,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(KIND, BNt);
+            const uint32_t idesc = make_idesc(KIND, BNt, p.a_fmt);
             int s = 0;
             uint32_t phase = 0;
             int as = 0;
@@ -383,13 +429,16 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t da = make_desc_sw128(smem_u32(s_a + (size_t)s * a_bytes));
-                    const uint64_t db = make_desc_sw128(smem_u32(s_b + (size_t)s * b_stride));
 #pragma unroll
-                    for (int k = 0; k < kKBlockBytes / 32; ++k) {
-                        // advance both operands by 32 bytes of K inside the swizzled row
-                        tc_mma<KIND>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int at = 0; at < ATOMS; ++at) {
+                        const uint64_t da = make_desc_sw128(smem_u32(s_a + (size_t)s * a_bytes + at * a_atom));
+                        const uint64_t db = make_desc_sw128(smem_u32(s_b + (size_t)s * b_stride + at * b_atom));
+#pragma unroll
+                        for (int k = 0; k < kKBlockBytes / 32; ++k) {
+                            // advance both operands by 32 bytes of K inside the swizzled row
+                            tc_mma<KIND>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                         (kb > 0 || at > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
                     if (++s == p.stages) {
@@ -405,7 +454,70 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 }
             }
         }
-    } else {
+    } else if (WF != WF_TMA && warp >= kXf0) {
+        // ---------------- transform warps: packed nibbles -> operand tile ----------------
+        // A work item is one 16-byte unit of a row (32 codes = one scale block of the codebook
+        // format); consecutive threads take consecutive units, so the reads of the raw tile are
+        // contiguous, and the writes follow the 128-byte swizzle (16-byte chunk index XOR row mod 8).
+        const int xt = threadIdx.x - kXf0 * 32;
+        int s = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.kblocks; ++kb) {
+                if (!mbar_wait(&rawfull[s], phase, s_abort, p.err_flag, 0x200)) {
+                    ok = false;
+                    break;
+                }
+                const unsigned char *raw = s_raw + (size_t)s * (kRawBytes + kScBytes);
+                unsigned char *dst = s_a + (size_t)s * a_bytes;
+#pragma unroll
+                for (int it = 0; it < (kTileN * 4) / (kXfWarps * 32); ++it) {
+                    const int item = xt + it * kXfWarps * 32;
+                    const int row = item >> 2, c = item & 3;
+                    const uint4 w = *reinterpret_cast<const uint4 *>(raw + item * 16);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                    if (WF == WF_I4) {
+                        // 16*q as int8: even codes of a word, then odd codes (the activation planes
+                        // carry the same order inside every group of eight k)
+                        uint32_t o[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            o[2 * j] = (ww[j] << 4) & 0xF0F0F0F0u;
+                            o[2 * j + 1] = ww[j] & 0xF0F0F0F0u;
+                        }
+                        unsigned char *r = dst + row * 128;
+                        *reinterpret_cast<uint4 *>(r + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(r + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        // fp16 of block scale x centroid, one rounding; the unit is one scale block
+                        const float bs = *reinterpret_cast<const float *>(raw + kRawBytes + row * 16 + c * 4);
+                        unsigned char *r = dst + (c >> 1) * a_atom + row * 128;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float lo = __fmul_rn(bs, s_cb[(ww[j] >> (8 * q)) & 0xFu]);
+                                const float hi = __fmul_rn(bs, s_cb[(ww[j] >> (8 * q + 4)) & 0xFu]);
+                                const __half2 v = __floats2half2_rn(lo, hi);
+                                h[q] = *reinterpret_cast<const uint32_t *>(&v);
+                            }
+                            *reinterpret_cast<uint4 *>(r + ((((c & 1) * 4 + j) ^ (row & 7)) << 4)) =
+                                make_uint4(h[0], h[1], h[2], h[3]);
+                        }
+                    }
+                }
+                fence_proxy_async();   // these stores are read by the tensor core (async proxy)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp < kXf0) {
         // ---------------- epilogue (8 warps: a TMEM lane quadrant each, two warps per quadrant
         // taking alternate 16-column chunks) ----------------
         pdl_wait();   // dq, rowsum and the output buffer belong to kernels before this one
@@ -437,7 +549,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     if (T == 1)
                         acc = __uint_as_float(r[0][j]);
                     else if (KIND == KIND_I8)
-                        acc = (float)(int)r[0][j] * 128.0f + (float)(int)r[1][j];
+                        acc = ((float)(int)r[0][j] * 128.0f + (float)(int)r[1][j]) * p.acc_scale;
                     else if (T == 3)
                         acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) +
                               __uint_as_float(r[T - 1][j]);
@@ -470,10 +582,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 
 // ---- host side -----------------------------------------------------------------------------------
 
-struct TcWeightMaps {
-    CUtensorMap w;
-};
-
 // cuTensorMapEncodeTiled is looked up through the runtime, so the library itself carries no
 // link-time dependency on libcuda (it must load, and fail cleanly, on a machine without a driver).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -482,7 +590,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 
 int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
-               const cuuint32_t *box) {
+               const cuuint32_t *box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B,
+               CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
     static EncodeTiledFn encode = nullptr;
     if (!encode) {
         void *fn = nullptr;
@@ -494,38 +603,47 @@ int encode_map(CUtensorMap *map, void *base, int rank, const cuuint64_t *dims, c
         encode = (EncodeTiledFn)fn;
     }
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode(map, dtype, (cuuint32_t)rank, base, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return set_error(FNN_ERR_DISPATCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return FNN_OK;
 }
 
-// Tensor map of the weight operand.  With the tile-major copy the tensor is [tiles * K blocks * 128
-// rows][128 bytes] and the box of (row tile nt, K block kb) starts at row (nt * kblocks + kb) * 128:
-// 16 KB of contiguous memory.  Without it (8-bit codes that were never prepared) the rows are read in
-// place, 128 bytes from each of 128 rows.
-int encode_weight_map(CUtensorMap *map, const fnn_cuda_qweight *w, int Kbytes) {
-    cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
-    if (w->tc) {
-        const size_t n_tiles = div_ceil(w->N, (size_t)kTileN);
-        cuuint64_t dims[2] = {(cuuint64_t)kKBlockBytes, (cuuint64_t)(n_tiles * w->tc_kblocks * kTileN)};
-        cuuint64_t strides[1] = {(cuuint64_t)kKBlockBytes};
-        return encode_map(map, w->tc, 2, dims, strides, box);
+// Tensor map of the weight operand over the packed rows (row stride ld_u4 * 16 bytes).
+//   I8 / FP8: 128 bytes x 128 rows per box, 128-byte swizzle: the operand tile itself.
+//   FP4:      the 4-bit type that unpacks sixteen codes (8 bytes) into every 16-byte slot: 128 codes
+//             x 128 rows per box, 128-byte swizzle.  Needs 32-byte aligned rows.
+//   I4 / I4CB: the packed nibbles as bytes, 64 bytes x 128 rows, unswizzled (the transform warps
+//             read them linearly).
+int encode_weight_map(CUtensorMap *map, const fnn_cuda_qweight *w) {
+    const cuuint64_t row_bytes = (cuuint64_t)w->ld_u4 * 16;
+    cuuint64_t strides[1] = {row_bytes};
+    if (w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) {
+        cuuint64_t dims[2] = {(cuuint64_t)w->K, (cuuint64_t)w->N};
+        cuuint32_t box[2] = {(cuuint32_t)kKBlockBytes, (cuuint32_t)kTileN};
+        return encode_map(map, (void *)w->rows, 2, dims, strides, box);
     }
-    cuuint64_t dims[2] = {(cuuint64_t)Kbytes, (cuuint64_t)w->N};
-    cuuint64_t strides[1] = {(cuuint64_t)w->ld_u4 * 16};
-    return encode_map(map, (void *)w->rows, 2, dims, strides, box);
+    if (w->fmt == FNN_FMT_F4) {
+        cuuint64_t dims[2] = {row_bytes * 2, (cuuint64_t)w->N};   // in codes; a multiple of 128
+        cuuint32_t box[2] = {128, (cuuint32_t)kTileN};
+        return encode_map(map, (void *)w->rows, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
+    }
+    cuuint64_t dims[2] = {row_bytes, (cuuint64_t)w->N};
+    cuuint32_t box[2] = {64, (cuuint32_t)kTileN};
+    return encode_map(map, (void *)w->rows, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // Scratch of one call: the rewritten activations Bq[T][Mpad][Kp], then dq[Mpad] and rowsum[Mpad].
 // `fixed_scratch` null: the context's growable buffer; otherwise a caller-supplied region of
 // `fixed_bytes` that must already be large enough (the entry point that may not allocate).
-template <int KIND, int T>
+template <int KIND, int T, int WF>
 int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = nullptr, size_t fixed_bytes = 0) {
     const fnn_cuda_qweight *w = a.w;
     constexpr int ES = (KIND == KIND_F16) ? 2 : 1;  // bytes per operand element
+    constexpr int ATOMS = (KIND == KIND_F16) ? 2 : 1;
     const int M = (int)a.M, N = (int)w->N, K = (int)w->K;
     const int Kbytes = K * ES;
     const int Kp = (Kbytes + 15) & ~15;  // row bytes; TMA strides are multiples of 16 bytes
@@ -559,18 +677,17 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
                        FNN_ERR_DISPATCH);
     // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
     // kernels makes every SM reconfigure (and drain) twice per call
-    FNN_CUDA_CHECK(cudaFuncSetAttribute(act_prep_kernel<KIND, T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    auto prep = act_prep_kernel<KIND, T, WF == WF_I4>;
+    FNN_CUDA_CHECK(cudaFuncSetAttribute(prep, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared),
                    FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(act_prep_kernel<KIND, T>, M, 256, 0, ctx->stream, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
+    FNN_CUDA_CHECK(launch_pdl(prep, M, 256, 0, ctx, a.a, M, K, Kp, Mpad, bq, dq, rowsum),
                    FNN_ERR_DISPATCH);
     ctx->launches++;
 
-    CUtensorMap map_w, map_a;
-    {
-        rc = encode_weight_map(&map_w, w, Kbytes);
-        if (rc != FNN_OK) return rc;
-    }
+    CUtensorMap map_w, map_a, map_s;
+    rc = encode_weight_map(&map_w, w);
+    if (rc != FNN_OK) return rc;
     {
         cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Mpad, (cuuint64_t)T};
         cuuint64_t strides[2] = {(cuuint64_t)Kp, (cuuint64_t)Kp * Mpad};
@@ -578,13 +695,24 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
         rc = encode_map(&map_a, bq, 3, dims, strides, box);
         if (rc != FNN_OK) return rc;
     }
+    if (WF == WF_CB) {
+        // block scales f32 [N][K/32] as bytes: four scales (16 bytes) per row and stage
+        cuuint64_t dims[2] = {(cuuint64_t)w->blocks_per_row * 4, (cuuint64_t)w->N};
+        cuuint64_t strides[1] = {(cuuint64_t)w->blocks_per_row * 4};
+        cuuint32_t box[2] = {16, (cuuint32_t)kTileN};
+        rc = encode_map(&map_s, (void *)w->scales, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != FNN_OK) return rc;
+    } else {
+        map_s = map_a;   // unused
+    }
 
     TcParams p{};
-    p.scales = (w->fmt == FNN_FMT_I4CB) ? nullptr : w->scales;  // block scales are folded into the copy
+    p.scales = (w->fmt == FNN_FMT_I4CB) ? nullptr : w->scales;  // block scales are folded into the operand
     p.zeros = w->zeros;
     p.bias = a.bias;
     p.dq = dq;
     p.rowsum = rowsum;
+    p.codebook = w->codebook;
     p.out = a.out;
     p.err_flag = ctx->err_flag;
     p.M = M;
@@ -593,143 +721,66 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     p.Mb = Mb;
     p.n_tiles = (N + kTileN - 1) / kTileN;
     p.m_tiles = m_tiles;
-    p.kblocks = (Kbytes + kKBlockBytes - 1) / kKBlockBytes;
-    p.tiled = w->tc != nullptr;
-    p.w_tiles = (const unsigned char *)w->tc;
+    p.kblocks = (Kbytes + kKBlockBytes * ATOMS - 1) / (kKBlockBytes * ATOMS);
+    p.a_fmt = (w->fmt == FNN_FMT_F4) ? kFmtE2M1 : kFmtE4M3;
+    p.acc_scale = (WF == WF_I4) ? 0.0625f : 1.0f;
     p.epilogue = a.epilogue;
-    const int a_bytes = kTileN * kKBlockBytes;
-    const int b_stride = (T * Mb * kKBlockBytes + 1023) & ~1023;
-    int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride));
+    const int a_bytes = ATOMS * kTileN * kKBlockBytes;
+    const int b_stride = ATOMS * ((T * Mb * kKBlockBytes + 1023) & ~1023);
+    const int raw_bytes = (WF == WF_TMA) ? 0 : kTileN * 64 + (WF == WF_CB ? kTileN * 16 : 0);
+    int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride + raw_bytes));
     stages = std::max(2, std::min(stages, 8));
     p.stages = stages;
-    const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride) + (2 * stages + 4) * 8 + 64;
+    const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride + raw_bytes) + (3 * stages + 4) * 8 + 64 + 64;
     const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
-    auto kern = qmm_tc_kernel<KIND, T>;
+    const int threads = (2 + kEpiWarps + (WF == WF_TMA ? 0 : kXfWarps)) * 32;
+    auto kern = qmm_tc_kernel<KIND, T, WF>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                    FNN_ERR_DISPATCH);
-    FNN_CUDA_CHECK(launch_pdl(kern, grid, kThreadsTc, smem, ctx->stream, map_w, map_a, p), FNN_ERR_DISPATCH);
+    FNN_CUDA_CHECK(launch_pdl(kern, grid, threads, smem, ctx, map_w, map_a, map_s, p), FNN_ERR_DISPATCH);
     ctx->launches++;
     ctx->last_path = fixed_scratch ? "tc-noalloc" : "tc";
     return FNN_OK;
 }
 
-// Position i of the tile-major copy -> (weight row n, byte offset inside the row's operand bytes).
-// Each 16 KB tile is stored the way the 128-byte swizzle lays it out in shared memory (16-byte chunk
-// index XOR row mod 8), so that one untiled bulk copy of 16 KB brings it in ready for the MMA.
-__device__ __forceinline__ void tile_pos(size_t i, size_t kblocks, size_t &n, size_t &byte) {
-    const size_t r = (i / kKBlockBytes) % kTileN;
-    const size_t bs = i % kKBlockBytes;
-    const size_t b = (((bs >> 4) ^ (r & 7)) << 4) | (bs & 15);
-    const size_t blk = i / ((size_t)kKBlockBytes * kTileN);   // nt * kblocks + kb
-    n = (blk / kblocks) * kTileN + r;
-    byte = (blk % kblocks) * kKBlockBytes + b;
-}
-
-// Codebook weights -> fp16 of blockscale * centroid (one rounding), tile-major, for kind::f16.
-__global__ void expand_codebook_kernel(const uint32_t *rows, size_t ld_words, size_t N, size_t K,
-                                       const float *bscales, size_t bpr, const float *codebook,
-                                       size_t kblocks, size_t total_halves, __half *out) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_halves; i += stride) {
-        size_t n, byte;
-        tile_pos(i * 2, kblocks, n, byte);
-        const size_t k = byte / 2;
-        float v = 0.0f;
-        if (n < N && k < K) {
-            const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
-            v = __fmul_rn(bscales[n * bpr + k / kCodebookBlock], codebook[nib]);
-        }
-        out[i] = __float2half_rn(v);
-    }
-}
-
-// 4-bit codes -> one byte per weight, exactly: e2m1 -> the e4m3 code of the same value,
-// two's-complement nibble -> int8; tile-major.
-__global__ void expand_nibbles_kernel(int fmt, const uint32_t *rows, size_t ld_words, size_t N, size_t K,
-                                      size_t kblocks, size_t total, uint8_t *out) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        size_t n, k;
-        tile_pos(i, kblocks, n, k);
-        uint8_t v = 0;
-        if (n < N && k < K) {
-            const uint32_t nib = (rows[n * ld_words + k / 8] >> (4 * (k % 8))) & 0xFu;
-            if (fmt == FNN_FMT_I4) {
-                v = (uint8_t)(int8_t)(((int32_t)(nib << 28)) >> 28);
-            } else {
-                // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 as e4m3 (bias 7, 3 mantissa bits)
-                const uint8_t lut[8] = {0x00, 0x30, 0x38, 0x3C, 0x40, 0x44, 0x48, 0x4C};
-                v = (uint8_t)(lut[nib & 7u] | ((nib & 8u) << 4));
-            }
-        }
-        out[i] = v;
-    }
-}
-
 }  // namespace
+
+int dispatch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed, size_t fixed_bytes);
 
 bool qmm_tc_supported(const fnn_cuda_qweight *w, size_t M) {
     (void)M;
-    // codes the tensor core takes natively (I8, FP8), after an exact one-byte expansion (I4, FP4),
-    // or -- the codebook format, whose block scales vary inside K -- as an fp16 copy of
-    // blockscale * centroid (only when those stay inside the fp16 range)
-    if (w->fmt == FNN_FMT_I4CB && !w->fp16_ok) return false;
+    // I8 / FP8 / FP4 codes are operands as stored; I4 and the codebook format are widened in shared
+    // memory.  The codebook format becomes fp16 of block scale x centroid (only when those stay inside
+    // the fp16 range) and its block scales travel by TMA, four per row and stage (K a multiple of 128).
+    if (w->fmt == FNN_FMT_I4CB && (!w->fp16_ok || w->K % 128 != 0)) return false;
     return w->K >= 128 && w->N >= 1 && w->N < (1u << 30) && w->K < (1u << 29);
 }
 
-int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w) {
-    // 8-bit codes are read in place from the rows (a tile-major copy measured within 4 % of that at
-    // every batch size and would double their footprint); the formats that need a byte or fp16
-    // expansion anyway get it tile-major
-    if (w->tc || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8) return FNN_OK;
-    FNN_REQUIRE(!ctx->capturing, FNN_ERR_MEMORY,
-                "first tcgen05 use of a weight happened during graph capture; run the plan once before "
-                "capturing it");
-    const size_t kbytes = (w->fmt == FNN_FMT_I4CB) ? w->K * 2 : w->K;   // operand bytes per row
-    const size_t kblocks = div_ceil(kbytes, (size_t)kKBlockBytes);
-    const size_t total = div_ceil(w->N, (size_t)kTileN) * kblocks * kTileN * kKBlockBytes;
-    void *buf = nullptr;
-    FNN_CUDA_CHECK(cudaMalloc(&buf, total), FNN_ERR_MEMORY);
-    const auto blocks_for = [&](size_t items) {
-        return (int)std::min<size_t>(div_ceil(items, 256), (size_t)ctx->sm_count * 16);
-    };
-    if (w->fmt == FNN_FMT_I4CB) {
-        expand_codebook_kernel<<<blocks_for(total / 2), 256, 0, ctx->stream>>>(
-            (const uint32_t *)w->rows, w->ld_u4 * 4, w->N, w->K, w->scales, w->blocks_per_row, w->codebook,
-            kblocks, total / 2, (__half *)buf);
-    } else {
-        expand_nibbles_kernel<<<blocks_for(total), 256, 0, ctx->stream>>>(
-            w->fmt, (const uint32_t *)w->rows, w->ld_u4 * 4, w->N, w->K, kblocks, total, (uint8_t *)buf);
-    }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        cudaFree(buf);
-        return set_error(FNN_ERR_DISPATCH, "tile-major copy: %s", cudaGetErrorString(e));
-    }
-    ctx->launches++;
-    w->tc = buf;
-    w->tc_bytes = total;
-    w->tc_kblocks = kblocks;
-    return FNN_OK;
-}
+// Nothing to build: every format is read from the packed rows.
+int prepare_qmm_tc(fnn_cuda_ctx *, fnn_cuda_qweight *) { return FNN_OK; }
 
-int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
-    FNN_REQUIRE(a.M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul: M=%zu too large for the tcgen05 path", a.M);
-    int rc = prepare_qmm_tc(ctx, const_cast<fnn_cuda_qweight *>(a.w));
-    if (rc != FNN_OK) return rc;
+// Format -> (MMA kind, activation terms, weight path).  `fixed`: caller-supplied scratch or null.
+int dispatch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed, size_t fixed_bytes) {
     switch (a.w->fmt) {
     case FNN_FMT_I8:
+        return launch_tc<KIND_I8, 2, WF_TMA>(ctx, a, fixed, fixed_bytes);
     case FNN_FMT_I4:
-        return launch_tc<KIND_I8, 2>(ctx, a);
+        return launch_tc<KIND_I8, 2, WF_I4>(ctx, a, fixed, fixed_bytes);
     case FNN_FMT_F8:
     case FNN_FMT_F4:
         // three e4m3 terms keep f32-grade accuracy while the scan of the weights is the bound;
         // two terms (~1e-3 of the output norm) once the tensor core is
-        return a.M >= 128 ? launch_tc<KIND_F8, 2>(ctx, a) : launch_tc<KIND_F8, 3>(ctx, a);
+        return a.M >= 128 ? launch_tc<KIND_F8, 2, WF_TMA>(ctx, a, fixed, fixed_bytes)
+                          : launch_tc<KIND_F8, 3, WF_TMA>(ctx, a, fixed, fixed_bytes);
     case FNN_FMT_I4CB:
-        return launch_tc<KIND_F16, 1>(ctx, a);
+        return launch_tc<KIND_F16, 1, WF_CB>(ctx, a, fixed, fixed_bytes);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
+}
+
+int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+    FNN_REQUIRE(a.M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul: M=%zu too large for the tcgen05 path", a.M);
+    return dispatch_tc(ctx, a, nullptr, 0);
 }
 
 }  // namespace fnn
@@ -759,13 +810,8 @@ extern "C" int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, 
                 "qmatmul_noalloc: unknown epilogue %d", epilogue);
     FNN_REQUIRE(((uintptr_t)a_dev & 15u) == 0 && ((uintptr_t)out_dev & 15u) == 0, FNN_ERR_DISPATCH,
                 "qmatmul_noalloc: pointers must be 16-byte aligned");
-    FNN_REQUIRE(qmm_tc_supported(w, M) && w->fmt != FNN_FMT_I4CB, FNN_ERR_UNSUPPORTED,
+    FNN_REQUIRE(qmm_tc_supported(w, M), FNN_ERR_UNSUPPORTED,
                 "qmatmul_noalloc: format %d / K=%zu is not served by this entry point", w->fmt, w->K);
-    // 4-bit formats read a byte-expanded copy that fnn_cuda_qweight_prepare(.., FNN_PATH_TC)
-    // builds; building it here would allocate
-    FNN_REQUIRE(w->tc != nullptr || w->fmt == FNN_FMT_I8 || w->fmt == FNN_FMT_F8, FNN_ERR_MEMORY,
-                "qmatmul_noalloc: call fnn_cuda_qweight_prepare(ctx, w, FNN_PATH_TC) once for 4-bit "
-                "weights before using the entry point that may not allocate");
     FNN_REQUIRE(M < (1u << 24), FNN_ERR_DISPATCH, "qmatmul_noalloc: M=%zu too large", M);
     if (M == 0) return FNN_OK;
     FNN_CUDA_CHECK(cudaSetDevice(ctx->device), FNN_ERR_DISPATCH);
@@ -777,14 +823,5 @@ extern "C" int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, 
     }
     uint8_t *scratch = (uint8_t *)g_noalloc_scratch_addr[ctx->device];
     QmmArgs args{w, a_dev, out_dev, bias_dev, M, epilogue};
-    switch (w->fmt) {
-    case FNN_FMT_I8:
-    case FNN_FMT_I4:
-        return launch_tc<KIND_I8, 2>(ctx, args, scratch, kNoAllocScratchBytes);
-    case FNN_FMT_F8:
-    case FNN_FMT_F4:
-        return M >= 128 ? launch_tc<KIND_F8, 2>(ctx, args, scratch, kNoAllocScratchBytes)
-                        : launch_tc<KIND_F8, 3>(ctx, args, scratch, kNoAllocScratchBytes);
-    }
-    return set_error(FNN_ERR_UNSUPPORTED, "qmatmul_noalloc: format %d", w->fmt);
+    return dispatch_tc(ctx, args, scratch, kNoAllocScratchBytes);
 }

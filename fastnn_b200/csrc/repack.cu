@@ -10,10 +10,8 @@ namespace fnn {
 void free_qweight_aux(fnn_cuda_qweight *w) {
     if (w->frag) cudaFree(w->frag);
     if (w->frag_bs) cudaFree(w->frag_bs);
-    if (w->tc) cudaFree(w->tc);
     w->frag = nullptr;
     w->frag_bs = nullptr;
-    w->tc = nullptr;
 }
 
 // One thread per element of the [N,K] result: unpack(q)*scale + zero, two roundings.
@@ -112,7 +110,10 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
     w->K = K;
     w->qblock = (fmt == FNN_FMT_I4CB) ? qblock : 0;
     w->words_per_row = wpr;
+    // rows are padded to 16 bytes; FP4 rows to 64 bytes (128 codes), which is what the 4-bit tensor-map
+    // type of the tcgen05 kernel addresses
     w->ld_u4 = div_ceil(wpr, 4);
+    if (fmt == FNN_FMT_F4) w->ld_u4 = div_ceil(w->ld_u4, 4) * 4;
     w->blocks_per_row = (fmt == FNN_FMT_I4CB) ? div_ceil(K, qblock) : 0;
 
     auto fail = [&](cudaError_t e, const char *what) {

@@ -82,6 +82,12 @@ int fnn_cuda_ctx_create(int device, fnn_cuda_ctx **out);   /* on a private non-b
 int fnn_cuda_ctx_create_on_stream(int device, void *stream, fnn_cuda_ctx **out);
 /* The `cudaStream_t` the context launches on (so that a caller can order its own work against it). */
 void *fnn_cuda_ctx_stream(fnn_cuda_ctx *ctx);
+/* Kernels are launched as programmatic dependents of the kernel before them on the stream: a
+ * kernel's prologue (weight prefetch, scales, barrier set-up) runs under its predecessor's tail and
+ * it waits only where it first touches what the predecessor wrote.  enabled == 0 turns that off
+ * for the launches that follow (every kernel then starts after the previous one has finished),
+ * which is how a launch is timed on its own. */
+int fnn_cuda_ctx_set_overlap(fnn_cuda_ctx *ctx, int enabled);
 int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx);
 int fnn_cuda_sync(fnn_cuda_ctx *ctx);
 /* Message of the last failing call on this thread ("" if none). */
@@ -132,9 +138,10 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
                             size_t N, size_t K, const float *scales, size_t n_scales,
                             const float *zeros, size_t n_zeros, size_t qblock,
                             const float *codebook16, fnn_cuda_qweight **out);
-/* Build the device layout a kernel family needs (fragment-major for FNN_PATH_MMA, tile-major
- * for FNN_PATH_TC; FNN_PATH_AUTO builds what automatic dispatch can pick for this shape) now
- * instead of at its first use.  Call it from Backend::compile, outside any graph capture. */
+/* Build the device layout a kernel family needs (fragment-major for FNN_PATH_MMA; the tcgen05
+ * kernel reads the packed rows and needs none; FNN_PATH_AUTO builds what automatic dispatch can
+ * pick for this shape) now instead of at its first use.  Call it from Backend::compile, outside any
+ * graph capture. */
 int fnn_cuda_qweight_prepare(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, int path);
 int fnn_cuda_qweight_free(fnn_cuda_qweight *w);
 /* Reference-layout byte count: (N*ceil(K/ITEMS) + 16) * 4. */
@@ -174,8 +181,8 @@ int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_
  * planes; 3 for FP8/FP4 below 128 batch rows) -- for example M = 512 at K = 4096, or M = 256 at
  * K = 8192.  A larger problem is refused with FNN_ERR_MEMORY and both sizes in the message.
  * a_dev [M,K], out_dev [M,N], bias_dev [N] or NULL are device pointers owned by the caller.
- * 4-bit weights need one earlier fnn_cuda_qweight_prepare(ctx, w, FNN_PATH_TC); the codebook
- * format is not served.  The first call on a device looks up the scratch array's device
+ * All five formats are served where the tcgen05 kernel is (K >= 128; the codebook format: K a
+ * multiple of 128).  The first call on a device looks up the scratch array's device
  * address; make that call before any stream capture.  All calls share the array and it keeps
  * the previous call's contents (the kernel clears what has to start at zero itself), so two
  * calls that overlap on the GPU -- different streams or contexts of one device -- race. */
