@@ -47,6 +47,8 @@ SIGNATURES = {
     "fnn_cuda_host_free": (_int, [_vp]),
     "fnn_cuda_qweight_upload": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _sz, _vp,
                                        _c.POINTER(_vp)]),
+    "fnn_cuda_qweight_from_arena": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _sz, _vp,
+                                           _c.POINTER(_vp)]),
     "fnn_cuda_qweight_prepare": (_int, [_vp, _vp, _int]),
     "fnn_cuda_qweight_free": (_int, [_vp]),
     "fnn_cuda_qweight_packed_bytes": (_sz, [_vp]),

@@ -318,9 +318,12 @@ class CudaBackend:
                                              ctypes.byref(mi), ctypes.byref(mem)))
         return {"sm_count": sm.value, "cc": (ma.value, mi.value), "total_mem": mem.value}
 
-    def upload_qweight(self, payload: bytes, meta: QuantizedWeightMeta) -> QWeightHandle:
-        """``get_or_cache_packed`` + ``packed_tensor_from_meta`` on the device."""
-        data = np.frombuffer(payload, dtype=np.uint8)
+    def upload_qweight(self, payload: bytes, meta: QuantizedWeightMeta, arena: Optional[CudaBuffer] = None,
+                       offset: int = 0, size: int = 0) -> QWeightHandle:
+        """``get_or_cache_packed`` + ``packed_tensor_from_meta`` on the device.  With ``arena`` the
+        payload is the WriteConst slot ``[offset, offset + size)`` already on the device (``payload``
+        is ignored): its rows are used in place or copied device-to-device."""
+        data = np.frombuffer(payload, dtype=np.uint8) if arena is None else None
         scales = np.ascontiguousarray(meta.scales, dtype=np.float32)
         zeros = np.ascontiguousarray(meta.zero_points, dtype=np.float32)
         cb = (np.ascontiguousarray(meta.codebooks[0], dtype=np.float32)
@@ -330,12 +333,13 @@ class CudaBackend:
                                f"quantized weight of rank {len(meta.shape)} (only MatMul weights)")
         n, k = meta.shape
         h = ctypes.c_void_p()
-        _check(self.lib.fnn_cuda_qweight_upload(
-            self.ctx, meta.fmt, data.ctypes.data, data.nbytes, n, k,
-            scales.ctypes.data if scales.size else None, scales.size,
-            zeros.ctypes.data if zeros.size else None, zeros.size,
-            meta.quant_block_size, cb.ctypes.data if cb is not None else None,
-            ctypes.byref(h)))
+        tail = (n, k, scales.ctypes.data if scales.size else None, scales.size,
+                zeros.ctypes.data if zeros.size else None, zeros.size, meta.quant_block_size,
+                cb.ctypes.data if cb is not None else None, ctypes.byref(h))
+        if arena is None:
+            _check(self.lib.fnn_cuda_qweight_upload(self.ctx, meta.fmt, data.ctypes.data, data.nbytes, *tail))
+        else:
+            _check(self.lib.fnn_cuda_qweight_from_arena(self.ctx, meta.fmt, arena.handle, offset, size, *tail))
         qw = QWeightHandle(self, h.value, meta)
         # build the kernel layouts now, so a later graph capture finds them in place
         _check(self.lib.fnn_cuda_qweight_prepare(self.ctx, h.value, self.path))
@@ -436,10 +440,10 @@ class CudaBackend:
         key = (w_slice.offset, w_slice.size)
         qw = arena.qweights.get(key)
         if qw is None:
-            # Lazily repack from the WriteConst bytes already in the arena, keyed by the weight
-            # slice like the CPU backend's packed-weight cache (src/backend/cpu/mod.rs:62-89).
-            payload = self.read_arena(arena, w_slice.offset, w_slice.size)
-            qw = self.upload_qweight(payload, meta)
+            # Lazily build the kernel layouts from the WriteConst bytes already in the arena (on the
+            # device: they never come back to the host), keyed by the weight slice like the CPU
+            # backend's packed-weight cache (src/backend/cpu/mod.rs:62-89).
+            qw = self.upload_qweight(b"", meta, arena, w_slice.offset, w_slice.size)
             arena.qweights[key] = qw
         epilogue = instr.params[3] if len(instr.params) > 3 else L.EPI_NONE
         bias_off = instr.input_slices[2].offset if len(instr.input_slices) > 2 else -1

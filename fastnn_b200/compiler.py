@@ -937,6 +937,13 @@ class AotExecutor:
                 for n in self.input_names]
         return self.executor.execute_profile(self.graph, self.plan, self.memory_plan, data)
 
+    def save(self, plan_path: str, memory_path: str) -> None:
+        """Write the compiled plan as `.fnnc` and its memory plan as JSON, the two files
+        `Runtime.load` reads (src/backend/runtime.rs:65-110).  The quantized weights go along as the
+        plan's WriteConst payloads and kernel metadata: loading never re-quantizes."""
+        from .runtime import Runtime
+        Runtime(self.executor.backend, self.plan, self.memory_plan).save(plan_path, memory_path)
+
     def memory_stats(self) -> Dict[str, int]:
         return {"arena_bytes": self.memory_plan.total_size,
                 "slots": len(self.memory_plan.slots)}

@@ -83,6 +83,7 @@ struct fnn_cuda_qweight {
     size_t words_per_row = 0;   // reference row length in u32
     size_t ld_u4 = 0;           // row stride of the row-padded layout, in 16-byte units
     uint4 *rows = nullptr;      // row-padded layout [N][ld_u4] (reference bit order)
+    bool rows_owned = true;     // false: `rows` points into the arena slot the payload was written to
     float *scales = nullptr;    // [N] (I4CB: [N][blocks_per_row])
     float *zeros = nullptr;     // [N] or nullptr when every zero point is 0
     float *codebook = nullptr;  // [16] for I4CB

@@ -108,10 +108,14 @@ struct FragSizing {
     int grid, tiles_per_group, Kc;
     size_t smem;
 };
+// `blocks_per_sm` > 1: several smaller blocks share an SM (each gets that fraction of the shared
+// memory), so that blocks of the next kernel on the stream become resident, and prefetch, as soon as
+// single blocks of this one retire.
 template <typename RowBytes>
 inline bool size_frag_launch(int sm_count, int ntiles, int groups, int Kpad, int kblk, size_t fixed,
-                             size_t per_tile, RowBytes act_bytes, FragSizing *out) {
-    const size_t cap = 226 * 1024;
+                             size_t per_tile, RowBytes act_bytes, FragSizing *out, int blocks_per_sm = 1) {
+    const size_t cap = (size_t)226 * 1024 / blocks_per_sm - (blocks_per_sm > 1 ? 1024 : 0);
+    sm_count *= blocks_per_sm;
     const size_t min_act = act_bytes(kblk * kChunkBlocks);
     if (fixed + per_tile + min_act > cap) return false;
     int grid = sm_count;

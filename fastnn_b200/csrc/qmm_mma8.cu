@@ -19,6 +19,8 @@
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
 #include "frag_common.cuh"
 
+#include <stdlib.h>
+
 namespace fnn {
 
 namespace {
@@ -127,7 +129,7 @@ struct P8 {
 // MULTI: more than one batch row (all rows scanned and staged together); the single-row instantiation
 // keeps the shortest prologue.  CG 8-column groups hold the (term, batch row) columns: up to 4 * CG rows.
 template <int FMT, int CG, int kG8, bool MULTI>
-__global__ void __launch_bounds__(kG8 * kW8 * 32, 1)
+__global__ void __launch_bounds__(kG8 * kW8 * 32, (kG8 == 1 && CG == 1 && !MULTI && !T8<FMT>::codebook) ? 3 : 1)
 qmm_mma8_kernel(P8 p) {
     using TT = T8<FMT>;
     constexpr int KBLK = TT::KBLK, MMAS = TT::MMAS;
@@ -521,7 +523,7 @@ qmm_mma8_kernel(P8 p) {
 }
 
 template <int FMT, int CG, int kG8, bool MULTI>
-int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
+int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a, int blocks_per_sm = 1) {
     using TT = T8<FMT>;
     const fnn_cuda_qweight *w = a.w;
     P8 p{};
@@ -553,7 +555,8 @@ int launch8(fnn_cuda_ctx *ctx, const QmmArgs &a) {
             return ((((size_t)cols * (kc + TT::PAD)) + 15) & ~(size_t)15) +
                    (TT::codebook ? (size_t)(kc / 32) * 8 * CG * 4 : 0);
         },
-        &sz);
+        &sz, blocks_per_sm);
+    if (!fits && blocks_per_sm > 1) return launch8<FMT, CG, kG8, MULTI>(ctx, a, 1);
     FNN_REQUIRE(fits, FNN_ERR_UNSUPPORTED,
                 "qmatmul: shared memory budget exceeded for M=%d on the 8-bit fragment kernel", p.M);
     p.tiles_per_group = sz.tiles_per_group;
@@ -576,9 +579,13 @@ int launch8_cg(fnn_cuda_ctx *ctx, const QmmArgs &a) {
     if (CG == 1) {
         const bool multi = a.M > 1;
         // (the codebook format keeps its two lookup tables in registers: two groups at most)
-        if constexpr (!T8<FMT>::codebook)
+        if constexpr (!T8<FMT>::codebook) {
+            // EXPERIMENT: single batch row as three independent one-group blocks per SM
+            static const int coresident = getenv("FNN_FRAG_CORESIDENT") ? atoi(getenv("FNN_FRAG_CORESIDENT")) : 0;
+            if (!multi && coresident > 1) return launch8<FMT, 1, 1, false>(ctx, a, coresident);
             if ((ntiles + 2) / 3 >= want)
                 return multi ? launch8<FMT, 1, 3, true>(ctx, a) : launch8<FMT, 1, 3, false>(ctx, a);
+        }
         if ((ntiles + 1) / 2 >= want)
             return multi ? launch8<FMT, 1, 2, true>(ctx, a) : launch8<FMT, 1, 2, false>(ctx, a);
         return multi ? launch8<FMT, 1, 1, true>(ctx, a) : launch8<FMT, 1, 1, false>(ctx, a);

@@ -52,10 +52,12 @@ using namespace fnn;
 
 extern "C" {
 
-int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size_t packed_bytes,
-                            size_t N, size_t K, const float *scales, size_t n_scales,
-                            const float *zeros, size_t n_zeros, size_t qblock,
-                            const float *codebook16, fnn_cuda_qweight **out) {
+// `packed_on_device`: the payload already sits in device memory (a WriteConst slot of the arena).  Its
+// rows are then used in place when their stride needs no padding, and copied device-to-device
+// otherwise; nothing travels through the host.
+static int qweight_build(fnn_cuda_ctx *ctx, int fmt, const void *packed, size_t packed_bytes, bool packed_on_device,
+                         size_t N, size_t K, const float *scales, size_t n_scales, const float *zeros,
+                         size_t n_zeros, size_t qblock, const float *codebook16, fnn_cuda_qweight **out) {
     clear_error();
     FNN_REQUIRE(ctx && out, FNN_ERR_DISPATCH, "qweight_upload: null argument");
     *out = nullptr;
@@ -124,13 +126,20 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
     };
     cudaError_t e;
     size_t row_bytes = w->ld_u4 * 16;
-    if ((e = cudaMalloc((void **)&w->rows, N * row_bytes)) != cudaSuccess) return fail(e, "cudaMalloc(rows)");
-    if (row_bytes != wpr * 4) {
-        if ((e = cudaMemset(w->rows, 0, N * row_bytes)) != cudaSuccess) return fail(e, "cudaMemset");
+    if (packed_on_device && row_bytes == wpr * 4 && ((uintptr_t)packed & 31u) == 0) {
+        // the arena slot is already [N][row_bytes]: read it where it is (the slot outlives the weight
+        // handle: constants persist for the life of the plan's arena)
+        w->rows = (uint4 *)packed;
+        w->rows_owned = false;
+    } else {
+        if ((e = cudaMalloc((void **)&w->rows, N * row_bytes)) != cudaSuccess) return fail(e, "cudaMalloc(rows)");
+        if (row_bytes != wpr * 4) {
+            if ((e = cudaMemset(w->rows, 0, N * row_bytes)) != cudaSuccess) return fail(e, "cudaMemset");
+        }
+        if ((e = cudaMemcpy2D(w->rows, row_bytes, packed, wpr * 4, wpr * 4, N,
+                              packed_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice)) != cudaSuccess)
+            return fail(e, "cudaMemcpy2D(rows)");
     }
-    if ((e = cudaMemcpy2D(w->rows, row_bytes, packed, wpr * 4, wpr * 4, N,
-                          cudaMemcpyHostToDevice)) != cudaSuccess)
-        return fail(e, "cudaMemcpy2D(rows)");
 
     // Expand per-tensor / per-group metadata to one entry per row (scale_for_row,
     // src/packed_tensor.rs:439-462), so kernels index by row only.
@@ -175,12 +184,36 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
     return FNN_OK;
 }
 
+int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size_t packed_bytes,
+                            size_t N, size_t K, const float *scales, size_t n_scales,
+                            const float *zeros, size_t n_zeros, size_t qblock,
+                            const float *codebook16, fnn_cuda_qweight **out) {
+    return qweight_build(ctx, fmt, packed, packed_bytes, false, N, K, scales, n_scales, zeros, n_zeros, qblock,
+                         codebook16, out);
+}
+
+int fnn_cuda_qweight_from_arena(fnn_cuda_ctx *ctx, int fmt, fnn_cuda_arena *arena, size_t offset,
+                                size_t packed_bytes, size_t N, size_t K, const float *scales, size_t n_scales,
+                                const float *zeros, size_t n_zeros, size_t qblock, const float *codebook16,
+                                fnn_cuda_qweight **out) {
+    clear_error();
+    FNN_REQUIRE(ctx && arena && out, FNN_ERR_DISPATCH, "qweight_from_arena: null argument");
+    FNN_REQUIRE((offset & 15u) == 0 && offset <= arena->bytes && packed_bytes <= arena->bytes - offset,
+                FNN_ERR_DISPATCH, "qweight_from_arena: weight slice [%zu, +%zu) outside arena of %zu bytes or "
+                "not 16-byte aligned", offset, packed_bytes, arena->bytes);
+    // the WriteConst that filled the slot was enqueued on this stream: it must have landed before a
+    // copy on another stream (cudaMemcpy2D) or the first kernel reads it
+    FNN_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), FNN_ERR_MEMORY);
+    return qweight_build(ctx, fmt, arena->base + offset, packed_bytes, true, N, K, scales, n_scales, zeros,
+                         n_zeros, qblock, codebook16, out);
+}
+
 int fnn_cuda_qweight_free(fnn_cuda_qweight *w) {
     if (!w) return FNN_OK;
     cudaSetDevice(w->ctx->device);
     cudaStreamSynchronize(w->ctx->stream);
     free_qweight_aux(w);
-    if (w->rows) cudaFree(w->rows);
+    if (w->rows && w->rows_owned) cudaFree(w->rows);
     if (w->scales) cudaFree(w->scales);
     if (w->zeros) cudaFree(w->zeros);
     if (w->codebook) cudaFree(w->codebook);

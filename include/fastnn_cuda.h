@@ -138,6 +138,16 @@ int fnn_cuda_qweight_upload(fnn_cuda_ctx *ctx, int fmt, const void *packed, size
                             size_t N, size_t K, const float *scales, size_t n_scales,
                             const float *zeros, size_t n_zeros, size_t qblock,
                             const float *codebook16, fnn_cuda_qweight **out);
+/* The same for a payload that Instruction::WriteConst has already written into the arena (what
+ * Backend::dispatch sees on the first execution): the packed rows are read where they are -- no copy,
+ * no trip through the host -- whenever their stride needs no padding (K a multiple of 32 codes; 128
+ * for FP4), and copied device-to-device otherwise.  The slot must stay untouched for the life of the
+ * handle, which the memory plan guarantees for constants
+ * (src/compiler/passes/memory_planning.rs:376-397). */
+int fnn_cuda_qweight_from_arena(fnn_cuda_ctx *ctx, int fmt, fnn_cuda_arena *arena, size_t offset,
+                                size_t packed_bytes, size_t N, size_t K, const float *scales,
+                                size_t n_scales, const float *zeros, size_t n_zeros, size_t qblock,
+                                const float *codebook16, fnn_cuda_qweight **out);
 /* Build the device layout a kernel family needs (fragment-major for FNN_PATH_MMA; the tcgen05
  * kernel reads the packed rows and needs none; FNN_PATH_AUTO builds what automatic dispatch can
  * pick for this shape) now instead of at its first use.  Call it from Backend::compile, outside any

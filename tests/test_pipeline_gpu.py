@@ -140,3 +140,25 @@ def test_unsupported_paths_fail_loudly(backend):
     with pytest.raises(fnn.BackendError, match="not implemented by the CUDA backend"):
         backend.dispatch(fnn.ExecutablePlan([bogus], 256), arena, fnn.ShapeEnv())
     arena.close()
+
+
+@pytest.mark.parametrize("quantize", [8, 4, "f8", "f4", "i4cb"])
+def test_saved_plan_runs_through_runtime_without_requantizing(backend, tmp_path, quantize):
+    """AotExecutor.save -> `.fnnc` + `.memory.json` -> Runtime.load on a CudaBackend -> run
+    (src/backend/runtime.rs:65-151): same bits as the executor that compiled the plan, twice (the
+    second run replays the plan without its WriteConst instructions)."""
+    m, k, n = 5, 512, 192
+    w, b, x = normal(70, (k, n), 0.02), normal(71, (n,), 0.01), normal(72, (m, k), 1.0)
+    nodes = [{"op_type": "Gemm", "inputs": "[x, w, b]", "outputs": "[h]"},
+             {"op_type": "Gelu", "inputs": "[h]", "outputs": "[y]"}]
+    aot = fnn.AotExecutor(nodes, {"w": w, "b": b}, ["x"], ["y"], {"x": [m, k]}, quantize=quantize,
+                          backend=backend)
+    want = aot.forward({"x": x})["y"]
+    aot.save(str(tmp_path / "m.fnnc"), str(tmp_path / "m.memory.json"))
+    rt = fnn.Runtime.load(backend, str(tmp_path / "m.fnnc"), str(tmp_path / "m.memory.json"))
+    try:
+        for _ in range(2):
+            got = np.frombuffer(rt.run([x.tobytes()])[0], np.float32).reshape(m, n)
+            assert np.array_equal(got, want)
+    finally:
+        rt.close()

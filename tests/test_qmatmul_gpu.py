@@ -406,6 +406,8 @@ TC_SHAPES = [(128, 128), (4096, 256), (1000, 200), (512, 1040), (8192, 384)]
 @pytest.mark.parametrize("kn", TC_SHAPES)
 def test_tcgen05_kernel_parity(backend, fmt, kn):
     k, n = kn
+    if fmt == orc.FMT_I4CB and k % 128:
+        pytest.skip("the codebook format's block scales reach the tcgen05 kernel four per row and stage")
     w = normal(150 + k + n, (k, n), 0.02)
     bias = normal(160 + n, (n,), 0.01)
     q = orc.quantize_kn(fmt, w)
