@@ -64,6 +64,9 @@ SIGNATURES = {
     "fnn_cuda_gather_wait": (_int, [_vp, _vp, _sz, _sz, _int, _sz, _vp]),
     "fnn_cuda_qmatmul_gather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
                                        _sz]),
+    "fnn_cuda_qmatmul_allgather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
+                                          _sz, _sz]),
+    "fnn_cuda_allgather_wait": (_int, [_vp, _vp, _sz, _int]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_rms_norm": (_int, [_vp, _vp, _sz, _sz, _c.c_longlong, _sz, _sz, _c.c_float, _sz]),
     "fnn_cuda_row_norm": (_int, [_vp, _vp, _int, _sz, _sz, _c.c_longlong, _c.c_longlong, _sz, _c.c_longlong, _sz,
@@ -71,6 +74,7 @@ SIGNATURES = {
     "fnn_cuda_softmax": (_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_memcpy": (_int, [_vp, _vp, _sz, _sz, _sz]),
     "fnn_cuda_fill": (_int, [_vp, _vp, _sz, _sz, _f]),
+    "fnn_cuda_memcpy2d": (_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_graph_begin": (_int, [_vp]),
     "fnn_cuda_graph_end": (_int, [_vp, _c.POINTER(_vp)]),
     "fnn_cuda_graph_launch": (_int, [_vp, _vp]),

@@ -455,6 +455,61 @@ class MemoryPlan:
 _ALIGN = 64  # memory_planning.rs:652-663
 
 
+def _byte_size_with_env(t: "TensorType", env: ShapeEnv) -> int:
+    """`TensorType::byte_size_with_env` (src/ir/node.rs:717-850) for f32 tensors: symbols take
+    their runtime value; quantized constants have no symbolic dimension."""
+    if t.dtype.is_quantized or not any(isinstance(d, str) for d in t.shape):
+        return t.byte_size()
+    n = 1
+    for d in t.shape:
+        n *= env.resolve(d)
+    return n * 4
+
+
+def tighten(memory_plan: "MemoryPlan", graph: "ComputeGraph", env: ShapeEnv) -> "MemoryPlan":
+    """`MemoryPlan::tighten` (src/compiler/passes/memory_planning.rs:44-236): shrink every slot
+    whose symbolic dimensions resolved to less than the planning maximum; offsets stay, the
+    total becomes the highest end of any slot.  A batch of 3 then needs 3 rows of every
+    activation slot instead of SYMBOL_DIM_MAX."""
+    slots, top = {}, 0
+    for nid, slot in memory_plan.slots.items():
+        node = graph.get_node(nid)
+        size = min(slot.size, max(_byte_size_with_env(node.output_type, env), 4)) if node is not None else slot.size
+        slots[nid] = Slot(slot.offset, size)
+        top = max(top, slot.offset + size)
+    return MemoryPlan(slots, max(top, _ALIGN), [(i, slots[i]) for i, _ in memory_plan.inputs],
+                      [(o, slots[o]) for o, _ in memory_plan.outputs])
+
+
+def tighten_slices(plan: ExecutablePlan, memory_plan: "MemoryPlan", tight: "MemoryPlan",
+                   env: ShapeEnv) -> ExecutablePlan:
+    """`tighten_slices` (src/backend/executor.rs:1194-1284): the instructions of `plan` with
+    every slice cut to its tightened slot and symbolic kernel params resolved."""
+    by_offset = {}
+    for nid, slot in memory_plan.slots.items():
+        by_offset[(slot.offset, slot.size)] = tight.slots[nid].size
+
+    def cut(s: BufferSlice) -> BufferSlice:
+        return BufferSlice(s.offset, by_offset.get((s.offset, s.size), s.size))
+
+    out = []
+    for ins in plan.instructions:
+        if isinstance(ins, CallKernel):
+            params = list(ins.params)
+            if ins.param_dims is not None and ins.kernel_name.startswith("matmul_"):
+                params[:3] = [env.resolve(d) for d in ins.param_dims[:3]]
+            out.append(CallKernel(ins.kernel_name, [cut(s) for s in ins.input_slices], cut(ins.output_slice),
+                                  params, ins.node_id, ins.param_dims, ins.weight_meta,
+                                  ins.secondary_output_slice))
+        elif isinstance(ins, MemCopy):
+            out.append(MemCopy(cut(ins.dst), cut(ins.src)))
+        elif isinstance(ins, Fill):
+            out.append(Fill(cut(ins.dst), ins.value))
+        else:
+            out.append(ins)
+    return ExecutablePlan(out, tight.total_size, list(plan.levels))
+
+
 def plan_memory(graph: ComputeGraph) -> MemoryPlan:
     """One slot per node at 64-byte aligned offsets; constants, inputs and outputs live for
     the whole execution (so weights persist across calls); an elementwise node reuses the slot
@@ -744,6 +799,22 @@ class GraphExecutor:
             raise BackendError("Dispatch", f"expected {len(graph.inputs)} inputs, "
                                            f"got {len(inputs)}")
         env = self.shape_env_from_inputs(graph, inputs)
+        if not graph.has_static_shapes():
+            # symbolic shapes: size the slots (and with them the arena) for this call's dimensions
+            # (src/backend/executor.rs:599-717); a later, larger call gets a larger arena and
+            # materialises the constants again
+            tight = tighten(memory_plan, graph, env)
+            plan = tighten_slices(plan, memory_plan, tight, env)
+            memory_plan = tight
+            have = self.cached_arena
+            if have is not None and getattr(have, "total_bytes", None) is None:
+                have_bytes = len(have)
+            else:
+                have_bytes = have.total_bytes if have is not None else 0
+            if have is not None and have_bytes < tight.total_size:
+                if hasattr(have, "close"):
+                    have.close()
+                self.cached_arena, self._static_plan = None, None
         first = self.cached_arena is None
         if first:
             self.cached_arena = self.backend.allocate_arena(memory_plan.total_size)
@@ -751,8 +822,9 @@ class GraphExecutor:
         for (nid, slot), data in zip(memory_plan.inputs, inputs):
             self.backend.write_arena(arena, slot.offset, data)
         run = plan
-        if not first and self._static_plan is not None:
-            run = self._static_plan
+        if not first:   # constants are in place: replay without WriteConst / Fill
+            run = ExecutablePlan([i for i in plan.instructions if not isinstance(i, (WriteConst, Fill))],
+                                 plan.arena_size, []) if not graph.has_static_shapes() else self._static_plan
         self.backend.dispatch(run, arena, env)
         if first:
             # Constants are materialised once; later calls replay the plan without

@@ -135,8 +135,8 @@ static int ctx_create(int device, bool use_given_stream, void *stream, fnn_cuda_
         }
         ctx->owns_stream = true;
     }
-    cudaError_t e = cudaMalloc((void **)&ctx->err_flag, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
+    cudaError_t e = cudaMalloc((void **)&ctx->err_flag, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, 2 * sizeof(int));
     if (e != cudaSuccess) {
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -457,6 +457,42 @@ int fnn_cuda_qmatmul_gather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float 
     return launch_qmm_mma(ctx, args);   // 8-bit operand kernel for I8 / I4 / FP4, fp16 kernel for the rest
 }
 
+int fnn_cuda_qmatmul_allgather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev, const float *bias_dev,
+                               size_t M, int epilogue, int rank, int world, void *const *peer_bases,
+                               size_t out_offset, size_t counter_offset, size_t n_total, size_t col0) {
+    clear_error();
+    FNN_REQUIRE(ctx && w && a_dev && peer_bases, FNN_ERR_DISPATCH, "qmatmul_allgather: null argument");
+    FNN_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, FNN_ERR_DISPATCH,
+                "qmatmul_allgather: rank %d of %d (at most 8 ranks of one node)", rank, world);
+    FNN_REQUIRE(col0 + w->N <= n_total && n_total < (1u << 30) && (out_offset & 15u) == 0 &&
+                    (counter_offset & 7u) == 0 && ((uintptr_t)a_dev & 15u) == 0,
+                FNN_ERR_DISPATCH, "qmatmul_allgather: columns [%zu, +%zu) outside a row of %zu, or misaligned offsets",
+                col0, w->N, n_total);
+    FNN_REQUIRE(epilogue >= FNN_EPI_NONE && epilogue <= FNN_EPI_SILU, FNN_ERR_DISPATCH,
+                "qmatmul_allgather: unknown epilogue %d", epilogue);
+    FNN_REQUIRE(M >= 1 && qmm_tc_supported(w, M), FNN_ERR_UNSUPPORTED,
+                "qmatmul_allgather: the tcgen05 kernel does not cover fmt=%d K=%zu", w->fmt, w->K);
+    AllGatherArgs g{};
+    for (int r = 0; r < world; ++r) {
+        FNN_REQUIRE(peer_bases[r] != nullptr, FNN_ERR_DISPATCH, "qmatmul_allgather: peer %d has no buffer", r);
+        g.peer_out[r] = (float *)((uint8_t *)peer_bases[r] + out_offset);
+        g.peer_arrive[r] = (unsigned *)((uint8_t *)peer_bases[r] + counter_offset);
+    }
+    g.ticket = ctx->err_flag + 1;
+    g.world = world;
+    g.n_total = (int)n_total;
+    g.col0 = (int)col0;
+    QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, nullptr, &g};
+    return launch_qmm_tc(ctx, args);
+}
+
+int fnn_cuda_allgather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t counter_offset, int world) {
+    clear_error();
+    FNN_REQUIRE(ctx && my_base && world >= 1 && world <= 8 && (counter_offset & 7u) == 0, FNN_ERR_DISPATCH,
+                "allgather_wait: bad argument");
+    return launch_allgather_wait(ctx, (unsigned *)((uint8_t *)my_base + counter_offset), world);
+}
+
 int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,
                          int world, size_t n_stride, void *out_dev) {
     clear_error();
@@ -520,6 +556,21 @@ int fnn_cuda_memcpy(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset,
     if (bytes == 0) return FNN_OK;
     FNN_CUDA_CHECK(cudaMemcpyAsync(arena->base + dst_offset, arena->base + src_offset, bytes,
                                    cudaMemcpyDeviceToDevice, ctx->stream),
+                   FNN_ERR_DISPATCH);
+    return FNN_OK;
+}
+
+int fnn_cuda_memcpy2d(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset, size_t dst_pitch,
+                      size_t src_offset, size_t src_pitch, size_t width, size_t rows) {
+    clear_error();
+    FNN_REQUIRE(ctx && arena, FNN_ERR_DISPATCH, "memcpy2d: null handle");
+    if (width == 0 || rows == 0) return FNN_OK;
+    FNN_REQUIRE(width <= dst_pitch && width <= src_pitch &&
+                    span_ok(arena, dst_offset, (rows - 1) * dst_pitch + width) &&
+                    span_ok(arena, src_offset, (rows - 1) * src_pitch + width),
+                FNN_ERR_DISPATCH, "memcpy2d: rows outside arena or wider than their pitch");
+    FNN_CUDA_CHECK(cudaMemcpy2DAsync(arena->base + dst_offset, dst_pitch, arena->base + src_offset, src_pitch,
+                                     width, rows, cudaMemcpyDeviceToDevice, ctx->stream),
                    FNN_ERR_DISPATCH);
     return FNN_OK;
 }

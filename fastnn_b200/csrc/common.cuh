@@ -64,7 +64,8 @@ struct fnn_cuda_ctx {
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     std::vector<void *> retired_scratch;   // outgrown scratch buffers (captured graphs may still name them)
-    int *err_flag = nullptr;  // device flag written by bounded waits that gave up
+    int *err_flag = nullptr;  // device flag written by bounded waits that gave up; err_flag[1]: CTA ticket of
+                              // the fused GEMM + all-gather
     bool overlap_launches = true;   // programmatic dependent launch (fnn_cuda_ctx_set_overlap)
 };
 
@@ -334,6 +335,16 @@ __device__ __forceinline__ void gather_finish(const GatherArgs &g, unsigned step
 }
 #endif
 
+// Fused GEMM + all-gather for any batch size (tcgen05 kernel): every rank stores its [M, n_local]
+// block into columns [col0, col0 + n_local) of every rank's [M, n_total] f32 output and, when its last
+// CTA is done, adds one to every rank's arrival counter (release at system scope).
+struct AllGatherArgs {
+    float *peer_out[8];          // every rank's [M, n_total] output
+    unsigned *peer_arrive[8];    // every rank's arrival counter
+    int *ticket;                 // local: CTAs of this launch that have finished
+    int world, n_total, col0;
+};
+
 struct QmmArgs {
     const fnn_cuda_qweight *w;
     const float *a;    // [M,K]
@@ -342,6 +353,7 @@ struct QmmArgs {
     size_t M;
     int epilogue;
     const GatherArgs *gather = nullptr;
+    const AllGatherArgs *allgather = nullptr;
 };
 
 int launch_qmm_rows(fnn_cuda_ctx *ctx, const QmmArgs &args);
@@ -352,6 +364,7 @@ bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M);
 int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &args);
 int launch_gather_wait(fnn_cuda_ctx *ctx, const unsigned long long *my_words, const unsigned *counters,
                        int world, int n_stride, float *out);
+int launch_allgather_wait(fnn_cuda_ctx *ctx, unsigned *counters, int world);
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 // shapes automatic dispatch sends to the skinny tensor-core kernel
 static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->K >= 512 && w->N >= 64; }

@@ -19,8 +19,6 @@
 // (src/backend/cpu/microkernels/gemm.rs:2048-2087, src/backend/cpu/matmul.rs:61-71).
 #include "frag_common.cuh"
 
-#include <stdlib.h>
-
 namespace fnn {
 
 namespace {
@@ -85,28 +83,48 @@ __device__ __forceinline__ void decode_f4(uint32_t w, uint32_t &plo, uint32_t &p
 //   I4CB (index into 16 centroids): every centroid is carried as v = 128*hi + lo, hi and lo in
 //   [0, 127], so a table byte never has its top bit set.  Indices 0..7 come out of one prmt on the
 //   raw word (indices 8..15 select "replicated top bit" = 0 there), indices 8..15 out of a second
-//   prmt on the word with every index's bit 3 flipped, and the two are OR-ed.
+//   prmt on the word with every index's bit 3 flipped (indices 0..7 give 0 there).  The two halves
+//   are not merged: each is an operand of its own MMA into the same accumulator, which costs tensor
+//   issue slots (idle here) instead of logic instructions (the limiter).
 struct CbTables {
     uint32_t hi[4], lo[4];   // bytes of entries 0-3, 4-7, 8-11, 12-15
 };
-__device__ __forceinline__ void decode_cb(const CbTables &t, uint32_t w, uint32_t &h0, uint32_t &h1,
-                                          uint32_t &l0, uint32_t &l1) {
+struct CbOperands {
+    uint32_t hi_a[2], hi_b[2], lo_a[2], lo_b[2];   // [codes 0..3 | codes 4..7]; _a: indices 0..7, _b: 8..15
+};
+__device__ __forceinline__ void decode_cb(const CbTables &t, uint32_t w, CbOperands &o) {
     const uint32_t f = w ^ 0x88888888u, w16 = w >> 16, f16 = f >> 16;
-    h0 = prmt(t.hi[0], t.hi[1], w) | prmt(t.hi[2], t.hi[3], f);       // codes 0..3 of the word
-    h1 = prmt(t.hi[0], t.hi[1], w16) | prmt(t.hi[2], t.hi[3], f16);   // codes 4..7
-    l0 = prmt(t.lo[0], t.lo[1], w) | prmt(t.lo[2], t.lo[3], f);
-    l1 = prmt(t.lo[0], t.lo[1], w16) | prmt(t.lo[2], t.lo[3], f16);
+    o.hi_a[0] = prmt(t.hi[0], t.hi[1], w);
+    o.hi_a[1] = prmt(t.hi[0], t.hi[1], w16);
+    o.hi_b[0] = prmt(t.hi[2], t.hi[3], f);
+    o.hi_b[1] = prmt(t.hi[2], t.hi[3], f16);
+    o.lo_a[0] = prmt(t.lo[0], t.lo[1], w);
+    o.lo_a[1] = prmt(t.lo[0], t.lo[1], w16);
+    o.lo_b[0] = prmt(t.lo[2], t.lo[3], f);
+    o.lo_b[1] = prmt(t.lo[2], t.lo[3], f16);
 }
 constexpr int kCbHalf = 8192;   // centroid c is carried as v = round(c / cmax * 8191) + 8192
 
-// Staged byte position of activation k inside its row.
+// Staged byte position of activation k inside its row: where its group of eight goes, plus its place
+// inside the group.  I4 reorders inside the group (0,2,4,6,1,3,5,7: even codes of a word, then odd);
+// the codebook format keeps the group but orders the sixteen groups of a 128-k block by (word c of a
+// scale block, scale block b) instead of (b, c), so that the 32 bytes one lane needs for the four MMAs
+// of a k-block are contiguous.
+template <int FMT>
+__device__ __forceinline__ int group_pos8(int k8) {   // k8: a multiple of 8
+    if (FMT == FNN_FMT_I4CB) {
+        const int r = k8 & 127, b = r >> 5, c = (r >> 3) & 3;
+        return (k8 & ~127) + c * 32 + b * 8;
+    }
+    return k8;
+}
+template <int FMT>
+__device__ __forceinline__ int inner_pos8(int i) {    // i in [0, 8)
+    return FMT == FNN_FMT_I4 ? ((i >> 1) + (i & 1) * 4) : i;
+}
 template <int FMT>
 __device__ __forceinline__ int act_pos8(int k) {
-    if (FMT == FNN_FMT_I4) {
-        const int i = k & 7;
-        return (k & ~7) | ((i >> 1) + (i & 1) * 4);  // 0,2,4,6,1,3,5,7
-    }
-    return k;
+    return group_pos8<FMT>(k & ~7) + inner_pos8<FMT>(k & 7);
 }
 
 struct P8 {
@@ -300,12 +318,13 @@ qmm_mma8_kernel(P8 p) {
                                 int q = __float2int_rn(e[j] * inv);
                                 q = max(-16256, min(16256, q));
                                 const int h = (q + 64) >> 7;
-                                const int pos = act_pos8<FMT>(j);   // position inside the 8-group
+                                const int pos = inner_pos8<FMT>(j);   // position inside the 8-group
                                 hi[pos >> 2] |= (uint32_t)(h & 0xFF) << ((pos & 3) * 8);
                                 lo[pos >> 2] |= (uint32_t)((q - h * 128) & 0xFF) << ((pos & 3) * 8);
                             }
-                            *reinterpret_cast<uint2 *>(s_act + (size_t)(mb + m) * RS + i8 * 8) = make_uint2(hi[0], hi[1]);
-                            *reinterpret_cast<uint2 *>(s_act + (size_t)(p.M + mb + m) * RS + i8 * 8) =
+                            const int gp = group_pos8<FMT>(i8 * 8);
+                            *reinterpret_cast<uint2 *>(s_act + (size_t)(mb + m) * RS + gp) = make_uint2(hi[0], hi[1]);
+                            *reinterpret_cast<uint2 *>(s_act + (size_t)(p.M + mb + m) * RS + gp) =
                                 make_uint2(lo[0], lo[1]);
                         }
                     }
@@ -356,19 +375,16 @@ qmm_mma8_kernel(P8 p) {
             // with an offset of 8192, which the second MMA of a block takes back through its C operand
             const int nblk = kc_len / 32;
             for (int i = tid; i < nblk * 8 * CG; i += NT) {
-                const int blk = i / (8 * CG), col = i - blk * (8 * CG);
+                const int blk = i / (8 * CG), col = i - blk * (8 * CG), kb = blk >> 2, b = blk & 3;
                 int sum = 0;
                 if (col < cols) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(s_act + (size_t)col * RS + blk * 32);
-                    const uint4 x = src[0], y = src[1];
-                    sum = __dp4a((int)x.x, 0x01010101, sum);
-                    sum = __dp4a((int)x.y, 0x01010101, sum);
-                    sum = __dp4a((int)x.z, 0x01010101, sum);
-                    sum = __dp4a((int)x.w, 0x01010101, sum);
-                    sum = __dp4a((int)y.x, 0x01010101, sum);
-                    sum = __dp4a((int)y.y, 0x01010101, sum);
-                    sum = __dp4a((int)y.z, 0x01010101, sum);
-                    sum = __dp4a((int)y.w, 0x01010101, sum);
+                    const unsigned char *src = s_act + (size_t)col * RS + kb * 128 + b * 8;
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {   // the block's eight bytes of each of its four words
+                        const uint2 x = *reinterpret_cast<const uint2 *>(src + c4 * 32);
+                        sum = __dp4a((int)x.x, 0x01010101, sum);
+                        sum = __dp4a((int)x.y, 0x01010101, sum);
+                    }
                 }
                 s_boff[i] = -kCbHalf * sum;
             }
@@ -382,7 +398,7 @@ qmm_mma8_kernel(P8 p) {
             issue_next();
             cp_async_wait<kS8 - 1>();
             const int ch = gw + j * kW8;
-#pragma unroll
+#pragma unroll(CB ? 1 : kU8)
             for (int u = 0; u < kU8; ++u) {
                 const int slot = c_st * UNITS + u * 2;
                 const uint4 wl = *reinterpret_cast<const uint4 *>(my_ring + (size_t)slot * 512);
@@ -390,32 +406,41 @@ qmm_mma8_kernel(P8 p) {
                 const int kb_s = min(ch * kU8 + u, KBc - 1);
                 if constexpr (CB) {
                     // The unit of lane (g, c) holds word c of the four 32-element blocks of this
-                    // k-block: block b is one MMA (hi operand) plus one (lo operand), eight codes of
-                    // rows g and g + 8 per lane, and its integer sum is scaled by the block scale of
-                    // each row, which sits in the ring slot of lane (g, b).
+                    // k-block: block b is two MMAs for the hi bytes of the centroids plus two for the lo
+                    // bytes, eight codes of rows g and g + 8 per lane, and its integer sum is scaled by the
+                    // block scale of each row, which sits in the ring slot of lane (g, b).
                     const uint32_t wl4[4] = {wl.x, wl.y, wl.z, wl.w}, wh4[4] = {wh.x, wh.y, wh.z, wh.w};
+                    const float4 bl4 = *reinterpret_cast<const float4 *>(my_ring_bs + slot * 32 + (lane & ~3));
+                    const float4 bh4 = *reinterpret_cast<const float4 *>(my_ring_bs + (slot + 1) * 32 + (lane & ~3));
+                    const float bs_lo[4] = {bl4.x, bl4.y, bl4.z, bl4.w}, bs_hi[4] = {bh4.x, bh4.y, bh4.z, bh4.w};
+                    const unsigned char *ap[CG];   // this lane's activation bytes: 8 per scale block
+                    const int *op[CG];             // -8192 * block sums of its two columns
+#pragma unroll
+                    for (int cg = 0; cg < CG; ++cg) {
+                        ap[cg] = s_act + (size_t)max(brow[cg], 0) * RS + kb_s * 128 + c * 32;
+                        op[cg] = s_boff + (size_t)kb_s * 4 * 8 * CG + cg * 8 + 2 * c;
+                    }
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        uint32_t ah[4], al[4];
-                        decode_cb(cbt, wl4[b], ah[0], ah[2], al[0], al[2]);   // row g
-                        decode_cb(cbt, wh4[b], ah[1], ah[3], al[1], al[3]);   // row g + 8
-                        const float bs_lo = my_ring_bs[slot * 32 + (lane & ~3) + b];
-                        const float bs_hi = my_ring_bs[(slot + 1) * 32 + (lane & ~3) + b];
-                        const int blk = kb_s * 4 + b;
+                        CbOperands rg, rh;   // row g, row g + 8
+                        decode_cb(cbt, wl4[b], rg);
+                        decode_cb(cbt, wh4[b], rh);
 #pragma unroll
                         for (int cg = 0; cg < CG; ++cg) {
-                            uint2 bb = make_uint2(0, 0);
-                            if (brow[cg] >= 0)
-                                bb = *reinterpret_cast<const uint2 *>(s_act + (size_t)brow[cg] * RS + blk * 32 + c * 8);
-                            const int2 off = *reinterpret_cast<const int2 *>(s_boff + blk * 8 * CG + cg * 8 + 2 * c);
+                            uint2 bb = *reinterpret_cast<const uint2 *>(ap[cg] + b * 8);
+                            if (brow[cg] < 0) bb = make_uint2(0u, 0u);
+                            const uint32_t b0 = bb.x, b1 = bb.y;
+                            const int2 off = *reinterpret_cast<const int2 *>(op[cg] + b * 8 * CG);
                             int dh[4] = {0, 0, 0, 0};
                             int dl[4] = {off.x, off.y, off.x, off.y};
-                            mma_s8(dh, ah[0], ah[1], ah[2], ah[3], bb.x, bb.y);
-                            mma_s8(dl, al[0], al[1], al[2], al[3], bb.x, bb.y);
-                            accf[cg][0] = fmaf(bs_lo, (float)(dh[0] * 128 + dl[0]), accf[cg][0]);
-                            accf[cg][1] = fmaf(bs_lo, (float)(dh[1] * 128 + dl[1]), accf[cg][1]);
-                            accf[cg][2] = fmaf(bs_hi, (float)(dh[2] * 128 + dl[2]), accf[cg][2]);
-                            accf[cg][3] = fmaf(bs_hi, (float)(dh[3] * 128 + dl[3]), accf[cg][3]);
+                            mma_s8(dh, rg.hi_a[0], rh.hi_a[0], rg.hi_a[1], rh.hi_a[1], b0, b1);
+                            mma_s8(dh, rg.hi_b[0], rh.hi_b[0], rg.hi_b[1], rh.hi_b[1], b0, b1);
+                            mma_s8(dl, rg.lo_a[0], rh.lo_a[0], rg.lo_a[1], rh.lo_a[1], b0, b1);
+                            mma_s8(dl, rg.lo_b[0], rh.lo_b[0], rg.lo_b[1], rh.lo_b[1], b0, b1);
+                            accf[cg][0] = fmaf(bs_lo[b], (float)(dh[0] * 128 + dl[0]), accf[cg][0]);
+                            accf[cg][1] = fmaf(bs_lo[b], (float)(dh[1] * 128 + dl[1]), accf[cg][1]);
+                            accf[cg][2] = fmaf(bs_hi[b], (float)(dh[2] * 128 + dl[2]), accf[cg][2]);
+                            accf[cg][3] = fmaf(bs_hi[b], (float)(dh[3] * 128 + dl[3]), accf[cg][3]);
                         }
                     }
                     continue;
@@ -580,9 +605,13 @@ int launch8_cg(fnn_cuda_ctx *ctx, const QmmArgs &a) {
         const bool multi = a.M > 1;
         // (the codebook format keeps its two lookup tables in registers: two groups at most)
         if constexpr (!T8<FMT>::codebook) {
-            // EXPERIMENT: single batch row as three independent one-group blocks per SM
-            static const int coresident = getenv("FNN_FRAG_CORESIDENT") ? atoi(getenv("FNN_FRAG_CORESIDENT")) : 0;
-            if (!multi && coresident > 1) return launch8<FMT, 1, 1, false>(ctx, a, coresident);
+            // A single batch row on a layer with one to three tiles per group runs as three independent
+            // one-group blocks per SM instead of one three-group block: blocks of the next kernel on the
+            // stream then take the place of single finished blocks and prefetch their weights under
+            // this kernel's tail (config 2: 9.8 -> 9.0 us per step).  Smaller layers lose more to the
+            // smaller blocks' repeated prologue than they gain, larger ones have no tail to speak of.
+            if (!multi && ntiles >= 3 * ctx->sm_count && ntiles < 9 * ctx->sm_count)
+                return launch8<FMT, 1, 1, false>(ctx, a, 3);
             if ((ntiles + 2) / 3 >= want)
                 return multi ? launch8<FMT, 1, 3, true>(ctx, a) : launch8<FMT, 1, 3, false>(ctx, a);
         }

@@ -99,12 +99,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
-// Pulls the box of a later pipeline step from HBM into L2 only: the shared-memory ring then has to
-// cover the latency of L2, not of DRAM, however few bytes of a stage are weights.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int c0, int c1) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
-                 : "memory");
-}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
                                             int c1, int c2) {
     asm volatile(
@@ -277,6 +271,7 @@ struct TcParams {
     int Mb;        // batch rows per tile
     int n_tiles, m_tiles;
     int kblocks;   // pipeline stages' worth of K: ceil(operand bytes per row / (128 * atoms))
+    AllGatherArgs ag;   // ag.world > 0: outputs go to every rank's gathered buffer
     int a_fmt;     // A operand format of kind::f8f6f4
     float acc_scale;   // 1/16 when the int8 operand carries 16*q (I4)
     int stages;
@@ -322,8 +317,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             // the MMA issuer waits for the activation tile (one arrival with a byte count) and, for the
-            // formats widened in shared memory, for the transform warp that owns the stage
-            mbar_init(&full[s], 1 + (WF == WF_TMA ? 0 : 1));
+            // formats widened in shared memory, for every transform warp
+            mbar_init(&full[s], 1 + (WF == WF_TMA ? 0 : kXfWarps));
             mbar_init(&empty[s], 1);
             mbar_init(&rawfull[s], 1);
         }
@@ -377,26 +372,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             };
             // bytes the copies of a stage report to its barrier; the unpacking 4-bit tensor-map type counts
             // the packed source bytes (half of the 16 KB tile it writes)
-            // weight boxes are requested into L2 `ahead` pipeline steps before they are loaded
-            const int ahead = 3 * p.stages;
-            int pf_tile = blockIdx.x, pf_kb = 0;
-            auto prefetch_next = [&]() {
-                if (pf_tile >= total_tiles) return;
-                const int nt = pf_tile / p.m_tiles;
-                if (WF == WF_TMA) {
-#pragma unroll
-                    for (int at = 0; at < ATOMS; ++at)
-                        tma_prefetch_2d(&map_w, (pf_kb * ATOMS + at) * kKBlockBytes, nt * kTileN);
-                } else {
-                    tma_prefetch_2d(&map_w, pf_kb * 64, nt * kTileN);
-                    if (WF == WF_CB) tma_prefetch_2d(&map_s, pf_kb * 16, nt * kTileN);
-                }
-                if (++pf_kb == p.kblocks) {
-                    pf_kb = 0;
-                    pf_tile += gridDim.x;
-                }
-            };
-            for (int i = 0; i < ahead; ++i) prefetch_next();
             const uint32_t full_tx =
                 (uint32_t)((WF == WF_TMA ? (p.a_fmt == kFmtE2M1 ? a_bytes / 2 : a_bytes) : 0) + ATOMS * b_bytes);
             // The weights do not depend on the kernel before this one on the stream, the activation
@@ -429,7 +404,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     mbar_expect_tx(&full[s], full_tx);
                     load_w(s, nt, kb);
                     load_b(s, mt, kb);
-                    prefetch_next();
                     if (++s == p.stages) {
                         s = 0;
                         phase ^= 1;
@@ -486,31 +460,27 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         }
     } else if (WF != WF_TMA && warp >= kXf0) {
         // ---------------- transform warps: packed nibbles -> operand tile ----------------
-        // Every pipeline stage has its own warp (stage s belongs to transform warp s; there are at most
-        // as many stages as transform warps), so that all stages in flight are widened at the same
-        // time -- a warp's latency chain (barrier, shared-memory loads, logic, stores, fence) overlaps
-        // with the other warps' -- while each warp still meets the phases of its barrier one after the
-        // other, which is what a parity wait needs.  A work item is one 16-byte
-        // unit of a row (32 codes = one scale block of the codebook format); consecutive lanes take
-        // consecutive units, so the reads of the raw tile are contiguous, and the writes follow the
-        // 128-byte swizzle (16-byte chunk index XOR row mod 8).
-        const int xw = warp - kXf0;
+        // All transform warps work on every pipeline step together (every warp meets every phase of
+        // every barrier in order, which is what a parity wait needs; letting warps run steps apart
+        // would let one of them see a barrier two phases behind and take it for ready).  A work item is
+        // one 16-byte unit of a row (32 codes = one scale block of the codebook format); consecutive
+        // threads take consecutive units, so the reads of the raw tile are contiguous, and the writes
+        // follow the 128-byte swizzle (16-byte chunk index XOR row mod 8).
+        const int xt = threadIdx.x - kXf0 * 32;
+        int s = 0;
+        uint32_t phase = 0;
         bool ok = true;
-        int step = 0;   // pipeline steps of this CTA so far: step -> stage step % stages, phase (step / stages) & 1
-        for (int tile = blockIdx.x; tile < total_tiles && ok && xw < p.stages; tile += gridDim.x) {
-            for (int kb = 0; kb < p.kblocks; ++kb, ++step) {
-                const int s = step % p.stages;
-                if (s != xw) continue;
-                const uint32_t phase = (uint32_t)(step / p.stages) & 1u;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.kblocks; ++kb) {
                 if (!mbar_wait(&rawfull[s], phase, s_abort, p.err_flag, 0x200)) {
                     ok = false;
                     break;
                 }
                 const unsigned char *raw = s_raw + (size_t)s * (kRawBytes + kScBytes);
                 unsigned char *dst = s_a + (size_t)s * a_bytes;
-#pragma unroll 4
-                for (int it = 0; it < (kTileN * 4) / 32; ++it) {
-                    const int item = lane + it * 32;
+#pragma unroll
+                for (int it = 0; it < (kTileN * 4) / (kXfWarps * 32); ++it) {
+                    const int item = xt + it * kXfWarps * 32;
                     const int row = item >> 2, c = item & 3;
                     const uint4 w = *reinterpret_cast<const uint4 *>(raw + item * 16);
                     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
@@ -548,6 +518,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 fence_proxy_async();   // these stores are read by the tensor core (async proxy)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full[s]);
+                if (++s == p.stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
             }
         }
     } else if (warp < kXf0) {
@@ -591,7 +565,14 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     const float dot = acc * p.dq[m];
                     const float v = finish_output_fast(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
                                                        p.bias != nullptr, bias, p.epilogue);
-                    if (n_ok) p.out[(size_t)m * p.N + n] = v;  // a warp writes 32 consecutive n
+                    if (n_ok) {   // a warp writes 32 consecutive n
+                        if (p.ag.world == 0) {
+                            p.out[(size_t)m * p.N + n] = v;
+                        } else {   // plain peer stores over NVLink (and one local store)
+                            const size_t at = (size_t)m * p.ag.n_total + p.ag.col0 + n;
+                            for (int r = 0; r < p.ag.world; ++r) p.ag.peer_out[r][at] = v;
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -611,6 +592,39 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols)
                      : "memory");
     }
+    if (p.ag.world > 0 && threadIdx.x == 32) {
+        // Every store of this CTA happened before the barrier above; the fence makes them visible
+        // system-wide before the ticket.  The last CTA of the launch then tells every rank that this
+        // rank's block has arrived: fence (it has seen every other CTA's ticket), then one release add
+        // per rank.
+        __threadfence_system();
+        const int ticket = atomicAdd(p.ag.ticket, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            *p.ag.ticket = 0;
+            __threadfence_system();
+            for (int r = 0; r < p.ag.world; ++r)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.ag.peer_arrive[r]) : "memory");
+        }
+    }
+}
+
+// Consumer side of the fused GEMM + all-gather: counters = {arrivals, consumed}.  Waits (bounded) until
+// `world` more arrivals than have been consumed are in, then advances `consumed`; both live in device
+// memory, so a captured graph can be replayed.
+__global__ void allgather_wait_kernel(unsigned *counters, int world, int *err_flag) {
+    if (threadIdx.x != 0) return;
+    const unsigned want = counters[1] + (unsigned)world;
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned got;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(counters) : "memory");
+        if ((int)(got - want) >= 0) break;
+        if (clock64() - t0 > kWaitCycles) {
+            atomicOr(err_flag, 0x400);
+            return;   // gives up without consuming: the next wait sees the same state
+        }
+    }
+    counters[1] = want;
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -758,11 +772,12 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     p.a_fmt = (w->fmt == FNN_FMT_F4) ? kFmtE2M1 : kFmtE4M3;
     p.acc_scale = (WF == WF_I4) ? 0.0625f : 1.0f;
     p.epilogue = a.epilogue;
+    if (a.allgather) p.ag = *a.allgather;
     const int a_bytes = ATOMS * kTileN * kKBlockBytes;
     const int b_stride = ATOMS * ((T * Mb * kKBlockBytes + 1023) & ~1023);
     const int raw_bytes = (WF == WF_TMA) ? 0 : kTileN * 64 + (WF == WF_CB ? kTileN * 16 : 0);
     int stages = (int)((200 * 1024) / (size_t)(a_bytes + b_stride + raw_bytes));
-    stages = std::max(2, std::min(stages, WF == WF_TMA ? 12 : kXfWarps));   // one transform warp per stage
+    stages = std::max(2, std::min(stages, 8));
     p.stages = stages;
     const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride + raw_bytes) + (3 * stages + 4) * 8 + 64 + 64;
     const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
@@ -809,6 +824,13 @@ int dispatch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed, size_t fixe
         return launch_tc<KIND_F16, 1, WF_CB>(ctx, a, fixed, fixed_bytes);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
+}
+
+int launch_allgather_wait(fnn_cuda_ctx *ctx, unsigned *counters, int world) {
+    allgather_wait_kernel<<<1, 32, 0, ctx->stream>>>(counters, world, ctx->err_flag);
+    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
+    ctx->launches++;
+    return FNN_OK;
 }
 
 int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {

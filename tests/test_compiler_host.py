@@ -191,6 +191,36 @@ def test_batch_rows_are_the_product_of_all_leading_dims(shape, rows):
     assert fnn.backend.resolve_params(call.params, call.param_dims, env, 3) == [rows, 64, 16]
 
 
+def test_tighten_shrinks_symbolic_slots_and_the_arena():
+    """memory_planning.rs:44-236 / executor.rs:1194-1284: at d1 = 3 an activation slot holds 3 rows,
+    not SYMBOL_DIM_MAX; offsets stay; a larger batch later gets a larger arena and its constants again."""
+    from fastnn_b200.compiler import tighten, tighten_slices
+    gb = GraphBuilder()
+    x = gb.input_with_dims(["d1", 64])
+    y = gb.silu(gb.matmul(x, gb.constant(normal(1, (64, 16), 0.02), TensorType.new([64, 16]))))
+    g = gb.to_graph()
+    g.inputs, g.outputs = gb.recorded_input_ids(), [y.node_id()]
+    be = RecordingBackend()
+    ex = GraphExecutor(be)
+    plan, mp, cg = ex.compile_with_weight_dtype(g, WeightDtype.I8)
+    env = fnn.ShapeEnv({"d1": 3})
+    tight = tighten(mp, cg, env)
+    assert {k: v.offset for k, v in tight.slots.items()} == {k: v.offset for k, v in mp.slots.items()}
+    out_id = cg.outputs[0]
+    assert mp.slots[out_id].size == fnn.backend.SYMBOL_DIM_MAX * 16 * 4 and tight.slots[out_id].size == 3 * 16 * 4
+    assert tight.total_size < mp.total_size
+    tplan = tighten_slices(plan, mp, tight, env)
+    call = [i for i in tplan.instructions if isinstance(i, fnn.CallKernel)][0]
+    assert call.params[:3] == [3, 64, 16] and call.output_slice.size == 3 * 16 * 4
+    ex.execute(cg, plan, mp, [bytes(3 * 64 * 4)])
+    small = len(be.arena)
+    assert small == tight.total_size < mp.total_size
+    ex.execute(cg, plan, mp, [bytes(2 * 64 * 4)])
+    assert len(be.arena) == small and be.dispatched[-1] == ["matmul_i8"]          # constants stay
+    ex.execute(cg, plan, mp, [bytes(50 * 64 * 4)])
+    assert len(be.arena) > small and be.dispatched[-1][0] == "WriteConst"          # regrown: constants again
+
+
 def test_quantize_argument_validation():
     assert WeightDtype.from_quantize(4) == WeightDtype.I4
     assert WeightDtype.from_quantize("i4cb") == WeightDtype.I4Codebook

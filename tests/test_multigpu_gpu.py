@@ -1,6 +1,7 @@
 """Column-sharded quantized Linear on 2 / 4 / 8 GPUs: the fused GEMV + peer-store all-gather kernel
-and the NCCL all-gather wrapper must both reproduce the unsharded oracle result on every rank.
-Needs that many CUDA devices (skipped otherwise); one process per GPU."""
+(up to four batch rows), the fused GEMM + all-gather on the tcgen05 kernel (any batch size, two
+layers chained) and the NCCL all-gather wrapper must all reproduce the unsharded oracle result on
+every rank.  Needs that many CUDA devices (skipped otherwise); one process per GPU."""
 import os
 
 import numpy as np
@@ -15,7 +16,7 @@ def _rank_main(rank, world, port, ret):
     import oracle as orc
     import fastnn_b200 as fnn
     from fastnn_b200 import _lib as L
-    from fastnn_b200.parallel import ColumnShardedLinear, FusedGatherLinear
+    from fastnn_b200.parallel import AllGatherLinear, ColumnShardedLinear, FusedGatherLinear, PeerArena
     from helpers import max_err_vs_rms, normal
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -23,7 +24,7 @@ def _rank_main(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     ok = True
     try:
-        backend = fnn.CudaBackend(rank, stream=torch.cuda.current_stream().cuda_stream)
+        backend = fnn.CudaBackend(rank)   # its own stream; the NCCL wrapper orders torch's stream against it
         k, n = 1024, 1000   # 1000 columns: shards of 500, not a multiple of the 16-row tile
         for fmt in (orc.FMT_I8, orc.FMT_I4, orc.FMT_F8, orc.FMT_F4, orc.FMT_I4CB):
             q = orc.quantize_kn(fmt, normal(31 + fmt, (k, n), 0.02))
@@ -57,6 +58,37 @@ def _rank_main(rank, world, port, ret):
             torch.cuda.synchronize()
             ok = ok and max_err_vs_rms(y.cpu().numpy(), orc.qmatmul(q, x)) <= 1e-2
             lin.weight.close()
+        # fused GEMM + all-gather on the tcgen05 kernel: two chained layers 1024 -> 1024 -> 1024, the
+        # second reading the rows the first one gathered; several steps reuse the same buffers
+        k = n = 1024
+        al = lambda v: -(-v // 256) * 256
+        m_max = 64
+        x_off, o1_off = 0, al(m_max * k * 4)
+        c1_off = o1_off + al(m_max * n * 4)
+        o2_off, c2_off = c1_off + 256, c1_off + 256 + al(m_max * n * 4)
+        b_off = c2_off + 256
+        pa = PeerArena(backend, b_off + al(n * 4), rank, world)
+        for fmt in (orc.FMT_I8, orc.FMT_I4, orc.FMT_F4):
+            q1 = orc.quantize_kn(fmt, normal(80 + fmt, (k, n), 0.02))
+            q2 = orc.quantize_kn(fmt, normal(90 + fmt, (n, n), 0.02))
+            bias = normal(95, (n,), 0.01)
+            mk = lambda q: fnn.QuantizedWeightMeta(bit_width=q.bit_width, scales=q.scales, zero_points=q.zeros,
+                                                   shape=[q.n, q.k], fmt=q.fmt)
+            l1 = AllGatherLinear(backend, q1.payload, mk(q1), rank, world, pa, o1_off, c1_off, L.EPI_SILU,
+                                 bias=bias, bias_off=b_off)
+            l2 = AllGatherLinear(backend, q2.payload, mk(q2), rank, world, pa, o2_off, c2_off, L.EPI_NONE)
+            for step, m in enumerate((64, 20, 64)):
+                x = normal(100 + step, (m, k), 1.0)
+                backend.write_arena(pa.arena, x_off, x.tobytes())
+                l1.forward(pa.device_ptr + x_off, m)
+                l2.forward(pa.device_ptr + o1_off, m)
+                backend.synchronize()   # raises if a bounded wait gave up
+                got = np.frombuffer(backend.read_arena(pa.arena, o2_off, m * n * 4), np.float32).reshape(m, n)
+                h = orc.qmatmul(q1, x, bias, orc.EPI_SILU)
+                ok = ok and max_err_vs_rms(got, orc.qmatmul(q2, h)) <= 2e-3
+            l1.close()
+            l2.close()
+        pa.close()
         backend.close()
     finally:
         ret[rank] = ok
