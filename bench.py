@@ -582,431 +582,6 @@ class FusedGatherLinearReplicas:
     def set_activations(self, x):
         self.backend.write_arena(self.arena, self.a_off, np.ascontiguousarray(x, np.float32).tobytes())
 
-    def launch(self, i, epi, path=0):
-        b = self.backend
-        rc = b.lib.fnn_cuda_qmatmul(b.ctx, self.weights[i % self.replicas].handle, self.arena.handle,
-                                    self.a_off, self.out_off, self.bias_off if self.has_bias else -1,
-                                    self.m, epi, path)
-        if rc != 0:
-            raise self.fnn.BackendError.from_status(rc)
-
-    def output(self):
-        raw = self.backend.read_arena(self.arena, self.out_off, self.m * self.n * 4)
-        return np.frombuffer(raw, np.float32).reshape(self.m, self.n)
-
-    def parity_err(self, epi, path=0, max_rows=64, width=64):
-        """One launch on fresh activations, checked against the CPU oracle on three slices of output
-        channels (first, middle, last `width`) and at most `max_rows` batch rows: max |err| / rms."""
-        import oracle as orc   # the checker: never inside a timed region
-        L, n, k, m = self.L, self.n, self.k, self.m
-        x = philox_normal(4242 + m, (m, k), 1.0)
-        self.set_activations(x)
-        self.launch(0, epi, path)
-        got = self.output()
-        width = min(width, n)
-        mid = (n // 2) // 16 * 16 + (8 if n >= 4 * width else 0)
-        rows = np.unique(np.concatenate([np.arange(0, width), np.arange(mid, min(mid + width, n)),
-                                         np.arange(n - width, n)]))
-        ms = np.arange(m) if m <= max_rows else np.arange(0, m, m // max_rows)[:max_rows]
-        wpr = -(-k // (4 if self.fmt in (L.FMT_I8, L.FMT_F8) else 8))
-        sub_words = np.concatenate([self.words[: n * wpr].reshape(n, wpr)[rows].reshape(-1),
-                                    np.zeros(16, np.uint32)])
-        if self.fmt == L.FMT_I4CB:
-            bpr = -(-k // 32)
-            sub = orc.QWeight(self.fmt, len(rows), k, sub_words,
-                              self.scales.reshape(n, bpr)[rows].reshape(-1).copy(), np.zeros(0, np.float32),
-                              self.cb, 32)
-        else:
-            sub = orc.QWeight(self.fmt, len(rows), k, sub_words, self.scales[rows].copy(),
-                              self.zp[rows].copy() if self.zp.size else np.zeros(0, np.float32))
-        want = orc.qmatmul(sub, x[ms], self.bias[rows] if self.has_bias else None, epi).astype(np.float64)
-        err = np.max(np.abs(got[np.ix_(ms, rows)] - want)) / max(np.sqrt(np.mean(want ** 2)), 1e-30)
-        return float(err)
-
-    def time_isolated(self, steps, epi, path=0):
-        """Per-launch time with programmatic dependent launch off: the same graph replay over the
-        rotating weight replicas, but every kernel starts only after the one before it has
-        finished, so no launch overlaps its neighbour's tail.  Returns ms per launch."""
-        lib, b = self.backend.lib, self.backend
-        check(lib.fnn_cuda_ctx_set_overlap(b.ctx, 0), self.fnn)
-        try:
-            return self.time_steps(steps, 3, epi, path) / steps
-        finally:
-            check(lib.fnn_cuda_ctx_set_overlap(b.ctx, 1), self.fnn)
-
-    def time_steps(self, steps, warmup, epi, path=0, min_seconds=0.0):
-        """CUDA-event time of `steps` launches replayed from one captured graph."""
-        b, lib = self.backend, self.backend.lib
-        for i in range(max(warmup, 1)):
-            self.launch(i, epi, path)
-        b.synchronize()
-        check(lib.fnn_cuda_graph_begin(b.ctx), self.fnn)
-        for i in range(steps):
-            self.launch(i, epi, path)
-        g = ctypes.c_void_p()
-        check(lib.fnn_cuda_graph_end(b.ctx, ctypes.byref(g)), self.fnn)
-        check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)  # graph warm-up (upload)
-        b.synchronize()
-        ms = ctypes.c_float()
-        check(lib.fnn_cuda_timer_start(b.ctx, 0), self.fnn)
-        check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)
-        check(lib.fnn_cuda_timer_stop(b.ctx, 0), self.fnn)
-        check(lib.fnn_cuda_timer_elapsed_ms(b.ctx, 0, ctypes.byref(ms)), self.fnn)
-        t_end = time.time() + min_seconds
-        while time.time() < t_end:  # untimed: keeps the same load up for the clock sampler
-            check(lib.fnn_cuda_graph_launch(b.ctx, g), self.fnn)
-            b.synchronize()
-        lib.fnn_cuda_graph_free(g)
-        return float(ms.value)
-
-    def close(self):
-        for w in self.weights:
-            w.close()
-        self.arena.close()
-
-
-def check(rc, fnn):
-    if rc != 0:
-        raise fnn.BackendError.from_status(rc)
-
-
-def run_e2e(fnn, backend, w_kn, steps, warmup):
-    """Public API, host buffers: AotExecutor.forward_pinned() = pinned H2D of x, the plan,
-    D2H of y, synchronize -- every step.  Executors rotate so weights still exceed L2."""
-    nodes = [{"op_type": "MatMul", "inputs": "[x, w]", "outputs": "[h]"},
-             {"op_type": "Silu", "inputs": "[h]", "outputs": "[y]"}]
-    n_exec = max(2, -(-3 * L2_BYTES // (K_DIM * N_DIM)))
-    execs = [fnn.AotExecutor(nodes, {"w": w_kn}, ["x"], ["y"], {"x": [M_HEAD, K_DIM]}, quantize=8,
-                             backend=backend) for _ in range(n_exec)]
-    xs = [philox_normal(100 + i, (M_HEAD, K_DIM), 1.0) for i in range(8)]
-    for e in execs:
-        e.forward({"x": xs[0]})  # first call materialises constants and captures the replay
-        e.bind_pinned()
-    for i in range(max(warmup, 3)):
-        e = execs[i % n_exec]
-        e.pinned_inputs["x"][...] = xs[i % 8]
-        e.forward_pinned()
-    launches0 = backend.launch_count()
-    t0 = time.perf_counter()
-    acc = 0.0
-    for i in range(steps):
-        e = execs[i % n_exec]
-        e.pinned_inputs["x"][...] = xs[i % 8]          # the step's input arrives in host memory
-        y = e.forward_pinned()["y"]
-        acc += float(y[0, 0])                           # the result is read on the host
-    dt = time.perf_counter() - t0
-    launches = backend.launch_count() - launches0
-    return dt / steps, launches, M_HEAD * K_DIM * 4, M_HEAD * N_DIM * 4, acc
-
-
-def cpu_baseline(w_kn, budget_s=12.0, max_iters=50):
-    """The oracle's restatement of gemm_batch_packed_simd, timed on this host."""
-    import oracle as orc
-    q = orc.quantize_kn(orc.FMT_I8, w_kn)
-    x = philox_normal(1, (M_HEAD, K_DIM), 1.0)
-    orc.qmatmul(q, x, None, orc.EPI_SILU)
-    times, t_all = [], time.perf_counter()
-    while len(times) < max_iters and time.perf_counter() - t_all < budget_s:
-        t = time.perf_counter()
-        orc.qmatmul(q, x, None, orc.EPI_SILU)
-        times.append(time.perf_counter() - t)
-    info = orc.host_info()
-    cores = info["physical_cores"] if M_HEAD >= info["physical_cores"] else 1
-    return float(np.median(times)), len(times), cores, info
-
-
-def sweep_points(L):
-    return [  # label, fmt, K, N, Ms, sigma, epilogue, bias
-        ("c2_i8", L.FMT_I8, 4096, 11008, (1, 4, 16, 128, 512), 0.02, L.EPI_SILU, False),
-        ("c1_i4", L.FMT_I4, 4096, 4096, (1, 8), 0.02, L.EPI_NONE, True),
-        ("c3_i4", L.FMT_I4, 8192, 28672, (1,), 0.015, L.EPI_NONE, False),
-        ("c3_f8", L.FMT_F8, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
-        ("c3_f4", L.FMT_F4, 8192, 28672, (1, 32, 512, 4096), 0.015, L.EPI_NONE, False),
-        ("c4_i4cb_up", L.FMT_I4CB, 2048, 8192, (1, 64), 0.02, L.EPI_GELU, True),
-        ("c4_i4cb_down", L.FMT_I4CB, 8192, 2048, (64,), 0.02, L.EPI_NONE, True),
-        ("i4cb_8192x8192", L.FMT_I4CB, 8192, 8192, (1,), 0.02, L.EPI_NONE, False),
-        ("c5_i4_gateup", L.FMT_I4, 4096, 28672, (64,), 0.02, L.EPI_NONE, False),
-        ("c5_i4_down", L.FMT_I4, 14336, 4096, (64,), 0.02, L.EPI_NONE, False),
-        ("c5_i4_qkv", L.FMT_I4, 4096, 6144, (64,), 0.02, L.EPI_NONE, False),
-    ]
-
-
-def run_sweep(fnn, backend, peaks, budget_s=420.0, only=None, only_m=None, steps_override=None,
-              path=0):
-    from fastnn_b200 import _lib as L
-    out, t_start = [], time.time()
-    cache = {}
-    for label, fmt, k, n, ms, sigma, epi, has_bias in sweep_points(L):
-        if only is not None:
-            if label != only:
-                continue
-            ms = tuple(m for m in ms if only_m is None or m == only_m) or (only_m,)
-        if time.time() - t_start > budget_s:
-            out.append({"point": label, "skipped": "sweep time budget"})
-            continue
-        key = (k, n, sigma)
-        if key not in cache:
-            cache.clear()
-            cache[key] = philox_normal(7, (k, n), sigma)
-        w = cache[key]
-        bias = philox_normal(8, (n,), 0.01) if has_bias else None
-        quantized = None
-        for m in ms:
-            layer = Layer(backend, fnn, fmt, w, m, bias, quantized=quantized)
-            quantized = layer.quantized
-            try:
-                err = layer.parity_err(epi, path)       # checked before it is timed
-                layer.set_activations(philox_normal(9, (m, k), 1.0))
-                est = max(layer.alg_bytes / 3e12, layer.flops / 2e13)
-                steps = steps_override or int(min(200, max(5, 0.05 / est)))
-                ms_total = layer.time_steps(steps, 3, epi, path)
-                t = ms_total / steps * 1e-3
-                iso = layer.time_isolated(steps, epi, path)
-                gbs, tfs = layer.alg_bytes / t / 1e9, layer.flops / t / 1e12
-                out.append({"point": label, "m": m, "k": k, "n": n, "path": backend.last_path(),
-                            "us": round(t * 1e6, 2), "isolated_us": round(iso * 1e3, 2),
-                            "gbs": round(gbs, 1), "tflops": round(tfs, 2),
-                            "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
-                            "tensor_frac_bf16": round(tfs / peaks["bf16_tflops"], 3),
-                            "parity_err": float(f"{err:.3g}")})
-            finally:
-                layer.close()
-    return out
-
-
-def run_ours(args):
-    import torch
-    import fastnn_b200 as fnn
-    from fastnn_b200 import _lib as L
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    backend = fnn.CudaBackend(local)   # its own non-blocking stream: CUDA graphs are captured on it
-    peaks = load_peaks()
-    if args.only:  # one sweep point only (profiling aid): prints that point and exits
-        pts = run_sweep(fnn, backend, peaks, only=args.only, only_m=args.only_m,
-                        steps_override=args.steps, path=args.path)
-        print(json.dumps({"sweep": pts}), flush=True)
-        backend.close()
-        return
-
-    # every rank owns an 11008-column shard (seeded by rank) of the [4096, 11008*world] layer
-    w_kn = philox_normal(1000 + rank, (K_DIM, N_DIM), SIGMA)
-    layer = Layer(backend, fnn, L.FMT_I8, w_kn, M_HEAD)
-    head_err = layer.parity_err(L.EPI_SILU)      # the timed kernel's output against the CPU oracle
-    layer.set_activations(philox_normal(1, (M_HEAD, K_DIM), 1.0))
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    t_load0 = time.time()
-    launches0 = backend.launch_count()
-    if world == 1:
-        ms_total = layer.time_steps(args.steps, args.warmup, L.EPI_SILU, min_seconds=1.5)
-        launches = args.steps
-    else:
-        ms_total, e2e_n = time_sharded(torch, dist, backend, layer, args, world, L)
-        launches = args.steps + 1 + e2e_n["launches"]
-    t_load1 = time.time()
-    clocks = sampler.stop(t_load0, t_load1) if rank == 0 else None
-    del launches0
-
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_n["s_per_step"]], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_n["s_per_step"] = float(t[0].item()), float(t[1].item())
-    per_step_s = ms_total / args.steps * 1e-3
-    total_bytes = layer.alg_bytes * world
-    value = total_bytes / per_step_s / 1e9
-    path = backend.last_path()
-
-    line = None
-    if rank == 0:
-        achieved = layer.alg_bytes / per_step_s / 1e9
-        line = {
-            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(per_step_s * 1e3, 6),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD,
-                       "m": M_HEAD, "k": K_DIM, "n_per_gpu": N_DIM, "format": "i8",
-                       "kernel_path": path, "parity_err": float(f"{head_err:.3g}"),
-                       "l2": f"weights rotate over {layer.replicas} replicas "
-                             f"({layer.replicas * K_DIM * N_DIM // 1000000} MB > 126 MB L2)",
-                       "parallelism": "single GPU" if world == 1 else
-                                      f"column-sharded x{world}; outputs all-gathered by the GEMV's own "
-                                      "peer stores over NVLink (no collective call)",
-                       "algorithmic_bytes_per_step_per_gpu": layer.alg_bytes},
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                         "traffic": NCU_TRAFFIC.get(("i8", K_DIM, N_DIM, M_HEAD), {}).get("bytes"),
-                         "traffic_source": NCU_TRAFFIC.get(("i8", K_DIM, N_DIM, M_HEAD), {}).get("source"),
-                         "peak_source": peaks["source"]},
-            "clocks": clocks, "gpu_launches": launches,
-        }
-    if world == 1:
-        iso_ms = layer.time_isolated(min(args.steps, 500), L.EPI_SILU)
-        line["isolated_us"] = round(iso_ms * 1e3, 2)
-        line["roofline"]["isolated_frac"] = round(layer.alg_bytes / (iso_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
-        line["roofline"]["note"] = ("achieved/frac: back-to-back replay of one CUDA graph (the next launch's "
-                                    "weight prefetch overlaps this one's tail); isolated_frac: one launch alone "
-                                    "on the stream after an L2 flush")
-        e2e_s, e2e_launches, h2d, d2h, _ = run_e2e(fnn, backend, w_kn, min(args.steps, 2000),
-                                                   args.warmup)
-        line["e2e"] = {"value": round(layer.alg_bytes / e2e_s / 1e9, 1), "unit": UNIT,
-                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "us_per_step": round(e2e_s * 1e6, 2),
-                       "api": "AotExecutor.forward_pinned (pinned H2D + plan + D2H + sync per step)"}
-        line["gpu_launches"] = launches + e2e_launches
-        t_med, iters, cores, info = cpu_baseline(w_kn)
-        line["cpu_baseline"] = {
-            "value": round(layer.alg_bytes / t_med / 1e9, 3), "unit": UNIT, "cores": cores,
-            "kind": "port",
-            "sample": f"the full M=1 layer, median of {iters} calls ({t_med * 1e3:.1f} ms each); "
-                      f"single-threaded as the reference is for M < cores; simd_level="
-                      f"{info['simd_level']}, k_tile={info['k_block_size']}"}
-        if not args.no_sweep:
-            line["sweep"] = run_sweep(fnn, backend, peaks)
-    else:
-        if rank == 0:
-            line["e2e"] = {"value": round(total_bytes / e2e_n["s_per_step"] / 1e9, 1), "unit": UNIT,
-                           "h2d_bytes_per_step": e2e_n["h2d"] * world, "d2h_bytes_per_step": e2e_n["d2h"] * world,
-                           "us_per_step": round(e2e_n["s_per_step"] * 1e6, 2),
-                           "api": "per rank and step one graph launch: pinned H2D of the activations, "
-                                  "fnn_cuda_qmatmul_gather, fnn_cuda_gather_wait (unpack), pinned D2H of the "
-                                  "gathered rows, synchronize"}
-    layer.close()
-    if not args.no_multi:
-        # the multi-GPU configurations, at every N (N = 1 gives the base of each curve)
-        strong = strong_scaling_c3(fnn, backend, rank, world, dist, peaks)
-        chain = c5_chain(fnn, backend, rank, world, dist)
-        if rank == 0:
-            line["strong_c3_f8_m1"] = strong
-            line["c5_chain"] = chain
-            line["gpu_launches"] += 100 + 3 * 32 * chain["launches_per_layer"]
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    backend.close()
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, keyed by (format, K, N, M), from ncu
-# captures of `python bench.py --only <point> --only-m <M>`; `source` names the kernel and the date
-# of the capture.  A point without an entry reports null.
-NCU_TRAFFIC = {
-    ("i8", 4096, 11008, 1): {"bytes": 45233920,
-                             "source": "qmm_mma8_kernel, ncu --set full, 2026-11-25: 45.2326 MB read + 1.3 KB written"},
-}
-
-
-def time_sharded(torch, dist, backend, layer, args, world, L):
-    """N > 1: every step is ONE kernel per rank -- the shard's GEMV whose epilogue stores its columns
-    into every rank's gathered buffer over NVLink peer memory as {value, step} words and which first
-    checks that the previous step has arrived from every peer (fnn_cuda_qmatmul_gather), replayed from
-    a CUDA graph that ends with fnn_cuda_gather_wait for the last step.  Barrier + synchronize on both
-    sides; CUDA events on the launching stream; the caller takes the max over ranks.  Returns the
-    device time in ms and the end-to-end (host buffers) measurement."""
-    import ctypes
-    rank = dist.get_rank()
-    lib = backend.lib
-    # one shared arena (gather buffers + flags); the layer's weight replicas rotate underneath it
-    fused = FusedGatherLinearReplicas(backend, layer, rank, world, L.EPI_SILU)
-    fused.set_activations(philox_normal(1, (layer.m, layer.k), 1.0))
-    for i in range(max(args.warmup, 3)):
-        fused.forward(i)
-    backend.synchronize()
-    dist.barrier()
-    check(lib.fnn_cuda_graph_begin(backend.ctx), layer.fnn)
-    for i in range(args.steps):
-        fused.forward(i)
-    fused.wait()   # the timed region ends only when the last step's shards have arrived from every peer
-    g = ctypes.c_void_p()
-    check(lib.fnn_cuda_graph_end(backend.ctx, ctypes.byref(g)), layer.fnn)
-    check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)   # graph warm-up on every rank
-    backend.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    ms = ctypes.c_float()
-    check(lib.fnn_cuda_timer_start(backend.ctx, 0), layer.fnn)
-    check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)
-    check(lib.fnn_cuda_timer_stop(backend.ctx, 0), layer.fnn)
-    check(lib.fnn_cuda_timer_elapsed_ms(backend.ctx, 0, ctypes.byref(ms)), layer.fnn)
-    backend.synchronize()
-    dist.barrier()
-    t_end = time.time() + 1.5
-    while time.time() < t_end:   # untimed: same load for the clock sampler, in lock step on all ranks
-        check(lib.fnn_cuda_graph_launch(backend.ctx, g), layer.fnn)
-        backend.synchronize()
-        flag = torch.tensor([1 if time.time() < t_end else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            break
-    lib.fnn_cuda_graph_free(g)
-    # end to end at N ranks: every step goes host -> device -> all ranks -> host (wall clock, barrier
-    # on both sides, max over ranks by the caller)
-    fused.bind_pinned()
-    xs = [philox_normal(100 + i, (layer.m, layer.k), 1.0) for i in range(8)]
-    e2e_steps = min(args.steps, 2000)
-    for i in range(max(args.warmup, 3)):
-        fused.x_host[...] = xs[i % 8].ravel()
-        fused.step_pinned(i)
-    dist.barrier()
-    t0 = time.perf_counter()
-    acc = 0.0
-    for i in range(e2e_steps):
-        fused.x_host[...] = xs[i % 8].ravel()
-        acc += float(fused.step_pinned(i)[0])
-    dist.barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    e2e = {"s_per_step": e2e_s, "steps": e2e_steps, "h2d": layer.m * layer.k * 4, "d2h": fused.plain_bytes,
-           "launches": 2 * e2e_steps}
-    fused.close()
-    return float(ms.value), e2e
-
-
-class FusedGatherLinearReplicas:
-    """bench-side driver of fnn_cuda_qmatmul_gather over the Layer's rotating weight replicas."""
-
-    def __init__(self, backend, layer, rank, world, dist):
-        import ctypes
-        self.backend, self.layer, self.rank, self.world = backend, layer, rank, world
-        self.n_stride = -(-layer.n // 4) * 4
-        word_bytes = 2 * world * 4 * self.n_stride * 8      # {value, step} words, two slots of 4 rows
-        self.counter_off = -(-word_bytes // 256) * 256
-        self.plain_off = self.counter_off + 256           # f32 [world][m][n_stride] written by wait()
-        self.plain_bytes = world * layer.m * self.n_stride * 4
-        self.a_off = self.plain_off + -(-self.plain_bytes // 256) * 256
-        self.arena = backend.allocate_arena(self.a_off + layer.m * layer.k * 4)
-        backend.synchronize()
-        handle = (ctypes.c_uint8 * 64)()
-        check(backend.lib.fnn_cuda_ipc_export(self.arena.handle, handle), layer.fnn)
-        handles = [None] * world
-        dist.all_gather_object(handles, bytes(handle))
-        self.graphs, self.pinned = [], []
-        self.peers = (ctypes.c_void_p * world)()
-        self.opened = []
-        for r in range(world):
-            if r == rank:
-                self.peers[r] = self.arena.device_ptr
-            else:
-                p = ctypes.c_void_p()
-                buf = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r])
-                check(backend.lib.fnn_cuda_ipc_open(backend.ctx, buf, ctypes.byref(p)), layer.fnn)
-                self.peers[r] = p.value
-                self.opened.append(p.value)
-        dist.barrier()
-
-    def set_activations(self, x):
-        self.backend.write_arena(self.arena, self.a_off, np.ascontiguousarray(x, np.float32).tobytes())
-
     def forward(self, i):
         layer, b = self.layer, self.backend
         rc = b.lib.fnn_cuda_qmatmul_gather(

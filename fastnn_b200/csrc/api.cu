@@ -137,6 +137,8 @@ static int ctx_create(int device, bool use_given_stream, void *stream, fnn_cuda_
     }
     cudaError_t e = cudaMalloc((void **)&ctx->err_flag, 2 * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->sk_flags, 2048 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->sk_flags, 0, 2048 * sizeof(unsigned));
     if (e != cudaSuccess) {
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -172,6 +174,7 @@ int fnn_cuda_ctx_destroy(fnn_cuda_ctx *ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     for (void *p : ctx->retired_scratch) cudaFree(p);
     if (ctx->err_flag) cudaFree(ctx->err_flag);
+    if (ctx->sk_flags) cudaFree(ctx->sk_flags);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return FNN_OK;

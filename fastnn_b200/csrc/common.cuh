@@ -67,6 +67,7 @@ struct fnn_cuda_ctx {
     int *err_flag = nullptr;  // device flag written by bounded waits that gave up; err_flag[1]: CTA ticket of
                               // the fused GEMM + all-gather
     bool overlap_launches = true;   // programmatic dependent launch (fnn_cuda_ctx_set_overlap)
+    unsigned *sk_flags = nullptr;   // 2 x 1024 zeroed counters of the tcgen05 kernel's split-K hand-over
 };
 
 struct fnn_cuda_arena {

@@ -99,6 +99,10 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first copy.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
                                             int c1, int c2) {
     asm volatile(
@@ -171,6 +175,28 @@ __host__ __device__ constexpr uint32_t make_idesc(int kind, int n_cols, int a_fm
 // generic-proxy writes to shared memory -> visible to the async proxy (the tensor core's reads)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// One activation, already divided by the row's step, as T narrow terms: an int8 pair hi * 128 + lo
+// (15 bits), or an e4m3 code followed by the codes of what the earlier terms left over.
+template <int KIND, int T>
+__device__ __forceinline__ void split_terms(float x, uint8_t t[3]) {
+    if (KIND == KIND_I8) {
+        int q = __float2int_rn(x);
+        q = max(-16256, min(16256, q));
+        const int hi = (q + 64) >> 7;
+        const int lo = q - hi * 128;
+        t[0] = (uint8_t)(int8_t)hi;
+        t[1] = (uint8_t)(int8_t)lo;
+    } else {
+        float r = x;
+#pragma unroll
+        for (int i = 0; i < T; ++i) {
+            __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+            t[i] = (uint8_t)c;
+            r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
+        }
+    }
+}
+
 // ---- activation rewrite ---------------------------------------------------------------------
 // One block per batch row.  Writes T byte planes Bq[t][m][Kp] (rows zero-padded to Kp), the
 // per-row factor dq[m] and the row sum.  PERM8: inside every group of eight k the bytes are stored
@@ -231,28 +257,145 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
         rowsum[m] = sum;
     }
     for (int k = tid; k < Kp; k += 256) {
-        const float x = (k < K) ? row[k] * inv : 0.0f;
         uint8_t t[3];
-        if (KIND == KIND_I8) {
-            int q = __float2int_rn(x);
-            q = max(-16256, min(16256, q));
-            int hi = (q + 64) >> 7;
-            int lo = q - hi * 128;
-            t[0] = (uint8_t)(int8_t)hi;
-            t[1] = (uint8_t)(int8_t)lo;
-        } else {
-            float r = x;
-#pragma unroll
-            for (int i = 0; i < T; ++i) {
-                __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-                t[i] = (uint8_t)c;
-                r -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));
-            }
-        }
+        split_terms<KIND, T>((k < K) ? row[k] * inv : 0.0f, t);
         const int i8 = k & 7;
         const int kk = PERM8 ? ((k & ~7) | ((i8 >> 1) + (i8 & 1) * 4)) : k;
 #pragma unroll
         for (int i = 0; i < T; ++i) bq[((size_t)i * Mpad + m) * Kp + kk] = t[i];
+    }
+}
+
+// The same rewrite for rows of a multiple of 8 and at most 16384 elements that start on 16 bytes
+// (every layer of a real model): the row is read once, eight consecutive elements per thread and
+// step with all loads in flight together, stays in registers between the scan and the rewrite, and
+// every plane is written eight bytes at a time.
+constexpr int kPrepHold = 8;   // units of eight elements a thread can hold
+template <int KIND, int T, bool PERM8>
+__global__ void __launch_bounds__(256)
+act_prep_regs_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
+                     float *__restrict__ dq, float *__restrict__ rowsum) {
+    __shared__ float s_max[8], s_sum[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const float4 *row4 = reinterpret_cast<const float4 *>(act + (size_t)m * K);
+    const int units = K >> 3;
+    float v[kPrepHold][8];
+#pragma unroll
+    for (int i = 0; i < kPrepHold; ++i) {
+        const int u = tid + i * 256;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (u < units) {
+            a = row4[2 * u];
+            b = row4[2 * u + 1];
+        }
+        v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+        v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+    }
+    float mx = 0.0f, sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kPrepHold; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            mx = fmaxf(mx, fabsf(v[i][j]));
+            sum += v[i][j];
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    }
+    if ((tid & 31) == 0) {
+        s_max[tid >> 5] = mx;
+        s_sum[tid >> 5] = sum;
+    }
+    __syncthreads();
+    mx = 0.0f;
+    sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        mx = fmaxf(mx, s_max[w]);
+        sum += s_sum[w];
+    }
+    if (KIND == KIND_F16) {
+        int ex = 15;
+        if (mx > 0.0f && isfinite(mx)) (void)frexpf(mx, &ex);
+        const int e = max(-120, min(120, 15 - ex));
+        const float up = ldexpf(1.0f, e);
+        if (tid == 0) {
+            dq[m] = ldexpf(1.0f, -e);
+            rowsum[m] = sum;
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(bq + (size_t)m * Kp);   // Kp = 2 K bytes here
+#pragma unroll
+        for (int i = 0; i < kPrepHold; ++i) {
+            const int u = tid + i * 256;
+            if (u >= units) continue;
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 x = __floats2half2_rn(v[i][2 * j] * up, v[i][2 * j + 1] * up);
+                h[j] = *reinterpret_cast<const uint32_t *>(&x);
+            }
+            dst[u] = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+        return;
+    }
+    const float full = (KIND == KIND_I8) ? 16256.0f : 448.0f;
+    const float step = (mx > 0.0f && isfinite(mx)) ? mx / full : 1.0f;
+    const float inv = 1.0f / step;
+    if (tid == 0) {
+        dq[m] = step;
+        rowsum[m] = sum;
+        if (Kp > K) {   // K is 8 mod 16: one more unit of zeros pads the row to 16 bytes
+#pragma unroll
+            for (int i = 0; i < T; ++i)
+                *reinterpret_cast<uint2 *>(bq + ((size_t)i * Mpad + m) * Kp + K) = make_uint2(0u, 0u);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kPrepHold; ++i) {
+        const int u = tid + i * 256;
+        if (u >= units) continue;
+        uint32_t w[T][2];
+#pragma unroll
+        for (int t = 0; t < T; ++t) w[t][0] = w[t][1] = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint8_t t[3];
+            split_terms<KIND, T>(v[i][j] * inv, t);
+            const int pos = PERM8 ? ((j >> 1) + (j & 1) * 4) : j;
+#pragma unroll
+            for (int q = 0; q < T; ++q) w[q][pos >> 2] |= (uint32_t)t[q] << (8 * (pos & 3));
+        }
+#pragma unroll
+        for (int q = 0; q < T; ++q)
+            *reinterpret_cast<uint2 *>(bq + ((size_t)q * Mpad + m) * Kp + (size_t)u * 8) = make_uint2(w[q][0], w[q][1]);
+    }
+}
+
+// The epilogue arithmetic of one chunk: 16 batch rows of one output channel.  `fac` carries the
+// rows' dq (lanes 0-15) and row sums (lanes 16-31).  No branches: EPI is a compile-time constant.
+template <int KIND, int T, int EPI>
+__device__ __forceinline__ void finish_chunk(const uint32_t (&r)[T][16], float fac, float scale, float zero,
+                                             float bias, bool has_bias, float acc_scale, float (&v)[16]) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float dq_m = __shfl_sync(0xFFFFFFFFu, fac, j);
+        const float rs_m = __shfl_sync(0xFFFFFFFFu, fac, 16 + j);
+        float acc;
+        if (T == 1)
+            acc = __uint_as_float(r[0][j]);
+        else if (KIND == KIND_I8)
+            acc = ((float)(int)r[0][j] * 128.0f + (float)(int)r[T > 1 ? 1 : 0][j]) * acc_scale;
+        else if (T == 3)
+            acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[T > 1 ? 1 : 0][j])) + __uint_as_float(r[T - 1][j]);
+        else
+            acc = __uint_as_float(r[0][j]) + __uint_as_float(r[T > 1 ? 1 : 0][j]);
+        // dot*scale + zero*sum(a) with the reference's separate roundings, then act(x + bias)
+        const float x = __fadd_rn(__fmul_rn(acc * dq_m, scale), __fmul_rn(zero, rs_m));
+        v[j] = apply_act_fast(has_bias ? __fadd_rn(x, bias) : x, EPI);
     }
 }
 
@@ -272,10 +415,49 @@ struct TcParams {
     int n_tiles, m_tiles;
     int kblocks;   // pipeline stages' worth of K: ceil(operand bytes per row / (128 * atoms))
     AllGatherArgs ag;   // ag.world > 0: outputs go to every rank's gathered buffer
+    // Work split along K as well as over tiles (layers with too few tiles to give every SM one): every CTA
+    // takes an equal, contiguous share of all (tile, K block) steps; where a share ends inside a tile
+    // the CTAs that hold the tile's later K blocks leave their raw accumulators in `sk_ws` and raise
+    // their flag, and the CTA that holds its first K block adds them up in CTA order and finishes it.
+    int sk_steps;        // steps per CTA; 0: every CTA takes whole tiles
+    float *sk_ws;        // [grid][T * Mb columns][128 rows] raw accumulators (int32 bits for kind::i8)
+    unsigned *sk_flags;  // [grid] epilogue warps of a CTA that have stored their part of its partial (0 .. 8);
+                         // [1024 + grid] epilogue warps of the finishing CTA that have consumed it
     int a_fmt;     // A operand format of kind::f8f6f4
     float acc_scale;   // 1/16 when the int8 operand carries 16*q (I4)
     int stages;
     int epilogue;
+};
+
+// The sequence of (tile, K block range) segments one CTA works through; every role of the CTA walks it
+// with its own copy.  Whole tiles, blockIdx.x + i * gridDim.x, when sk_steps == 0; otherwise the
+// CTA's contiguous share [blockIdx.x * sk_steps, +sk_steps) of the linear (tile, K block) space, cut
+// at tile boundaries.
+struct Segments {
+    int kblocks, total_tiles, sk_steps;
+    long long cur, end;   // linear step range (split mode)
+    int tile;             // next tile (whole-tile mode)
+    __device__ Segments(const TcParams &p, int total) : kblocks(p.kblocks), total_tiles(total), sk_steps(p.sk_steps) {
+        cur = (long long)blockIdx.x * sk_steps;
+        end = min(cur + sk_steps, (long long)total * kblocks);
+        tile = blockIdx.x;
+    }
+    __device__ bool next(int &t, int &kb0, int &kb1) {
+        if (sk_steps == 0) {
+            if (tile >= total_tiles) return false;
+            t = tile;
+            kb0 = 0;
+            kb1 = kblocks;
+            tile += gridDim.x;
+            return true;
+        }
+        if (cur >= end) return false;
+        t = (int)(cur / kblocks);
+        kb0 = (int)(cur - (long long)t * kblocks);
+        kb1 = (int)min((long long)kblocks, kb0 + (end - cur));
+        cur += kb1 - kb0;
+        return true;
+    }
 };
 
 // ATOMS: 128-byte swizzle atoms of K per pipeline stage (2 for fp16 operands: a stage is 128 k for
@@ -314,7 +496,31 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     uint32_t ncols = 32;
     while ((int)ncols < 2 * BNt) ncols <<= 1;
 
+    const int total_tiles = p.n_tiles * p.m_tiles;
+    // weights of stage `st`: the operand tile itself, or the packed nibbles (+ block scales) for the
+    // transform warps
+    auto load_w = [&](int st, int nt, int kb) {
+        if (WF == WF_TMA) {
+#pragma unroll
+            for (int at = 0; at < ATOMS; ++at)
+                tma_load_2d(s_a + (size_t)st * a_bytes + at * a_atom, &map_w, &full[st],
+                            (kb * ATOMS + at) * kKBlockBytes, nt * kTileN);
+        } else {
+            unsigned char *raw = s_raw + (size_t)st * (kRawBytes + kScBytes);
+            mbar_expect_tx(&rawfull[st], (uint32_t)(kRawBytes + kScBytes));
+            tma_load_2d(raw, &map_w, &rawfull[st], kb * 64, nt * kTileN);
+            if (WF == WF_CB) tma_load_2d(raw + kRawBytes, &map_s, &rawfull[st], kb * 16, nt * kTileN);
+        }
+    };
+    // bytes the copies of a stage report to its barrier; the unpacking 4-bit tensor-map type counts
+    // the packed source bytes (half of the 16 KB tile it writes)
+    const uint32_t full_tx =
+        (uint32_t)((WF == WF_TMA ? (p.a_fmt == kFmtE2M1 ? a_bytes / 2 : a_bytes) : 0) + ATOMS * b_bytes);
+
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
+        if (WF == WF_CB) prefetch_tensormap(&map_s);
         for (int s = 0; s < p.stages; ++s) {
             // the MMA issuer waits for the activation tile (one arrival with a byte count) and, for the
             // formats widened in shared memory, for every transform warp
@@ -328,20 +534,33 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // This thread is the TMA producer.  The weights do not depend on the kernel before this one on
+        // the stream: the first ring of weight tiles is requested here, before the rest of the CTA
+        // has finished setting up and before griddepcontrol.wait; the matching activation tiles
+        // follow in the producer's loop.
+        Segments segs(p, total_tiles);
+        int tile, kb0, kb1;
+        if (segs.next(tile, kb0, kb1)) {
+            const int head = min(p.stages, kb1 - kb0), nt = tile / p.m_tiles;
+            for (int i = 0; i < head; ++i) {
+                mbar_expect_tx(&full[i], full_tx);   // stage i: all stages start empty
+                load_w(i, nt, kb0 + i);
+            }
+        }
     }
-    if (WF == WF_CB && threadIdx.x >= 32 && threadIdx.x < 48) s_cb[threadIdx.x - 32] = p.codebook[threadIdx.x - 32];
-    if (warp == 0) {
+    if (WF == WF_CB && threadIdx.x >= 64 && threadIdx.x < 80) s_cb[threadIdx.x - 64] = p.codebook[threadIdx.x - 64];
+    if (warp == 1) {   // the MMA warp owns the tensor memory: it allocates and frees it
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(s_tmem)),
                      "r"(ncols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    __syncwarp();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
-    const int total_tiles = p.n_tiles * p.m_tiles;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -349,43 +568,23 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            // weights of stage `st`: the operand tile itself, or the packed nibbles (+ block scales)
-            // for the transform warps
-            auto load_w = [&](int st, int nt, int kb) {
-                if (WF == WF_TMA) {
-#pragma unroll
-                    for (int at = 0; at < ATOMS; ++at)
-                        tma_load_2d(s_a + (size_t)st * a_bytes + at * a_atom, &map_w, &full[st],
-                                    (kb * ATOMS + at) * kKBlockBytes, nt * kTileN);
-                } else {
-                    unsigned char *raw = s_raw + (size_t)st * (kRawBytes + kScBytes);
-                    mbar_expect_tx(&rawfull[st], (uint32_t)(kRawBytes + kScBytes));
-                    tma_load_2d(raw, &map_w, &rawfull[st], kb * 64, nt * kTileN);
-                    if (WF == WF_CB) tma_load_2d(raw + kRawBytes, &map_s, &rawfull[st], kb * 16, nt * kTileN);
-                }
-            };
             auto load_b = [&](int st, int mt, int kb) {
 #pragma unroll
                 for (int at = 0; at < ATOMS; ++at)
                     tma_load_3d(s_b + (size_t)st * b_stride + at * b_atom, &map_a, &full[st],
                                 (kb * ATOMS + at) * kKBlockBytes, mt * p.Mb, 0);
             };
-            // bytes the copies of a stage report to its barrier; the unpacking 4-bit tensor-map type counts
-            // the packed source bytes (half of the 16 KB tile it writes)
-            const uint32_t full_tx =
-                (uint32_t)((WF == WF_TMA ? (p.a_fmt == kFmtE2M1 ? a_bytes / 2 : a_bytes) : 0) + ATOMS * b_bytes);
-            // The weights do not depend on the kernel before this one on the stream, the activation
-            // planes do: the first ring of weight tiles is requested before griddepcontrol.wait, the
-            // matching activation tiles after it.
-            const int head = (blockIdx.x < total_tiles) ? min(p.stages, p.kblocks) : 0;
+            // The first ring of weight tiles is already on its way (requested during set-up); the
+            // activation planes depend on the kernel before this one: their tiles follow
+            // griddepcontrol.wait.
+            Segments segs(p, total_tiles);
+            int tile, kb0, kb1;
+            bool have = segs.next(tile, kb0, kb1);
+            const int head = have ? min(p.stages, kb1 - kb0) : 0;
             if (head > 0) {
-                const int nt = blockIdx.x / p.m_tiles, mt = blockIdx.x - nt * p.m_tiles;
-                for (int kb = 0; kb < head; ++kb) {
-                    mbar_expect_tx(&full[kb], full_tx);   // stage kb: all stages start empty
-                    load_w(kb, nt, kb);
-                }
+                const int mt = tile % p.m_tiles;
                 pdl_wait();
-                for (int kb = 0; kb < head; ++kb) load_b(kb, mt, kb);
+                for (int i = 0; i < head; ++i) load_b(i, mt, kb0 + i);
                 s = head;
                 if (s == p.stages) {
                     s = 0;
@@ -394,9 +593,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             } else {
                 pdl_wait();
             }
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            bool first = true;
+            for (; have && ok; have = segs.next(tile, kb0, kb1)) {
                 const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-                for (int kb = (tile == (int)blockIdx.x ? head : 0); kb < p.kblocks; ++kb) {
+                for (int kb = kb0 + (first ? head : 0); kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[s], phase ^ 1, s_abort, p.err_flag, 0x10)) {
                         ok = false;
                         break;
@@ -409,6 +609,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         phase ^= 1;
                     }
                 }
+                first = false;
             }
             if (!ok) {  // let copies already in flight land before the CTA can exit
                 for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -423,11 +624,13 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             int as = 0;
             uint32_t aphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            Segments segs(p, total_tiles);
+            int tile, kb0, kb1;
+            while (ok && segs.next(tile, kb0, kb1)) {
                 if (!mbar_wait(&tempty[as], aphase ^ 1, s_abort, p.err_flag, 0x20)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * BNt);
-                for (int kb = 0; kb < p.kblocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full[s], phase, s_abort, p.err_flag, 0x40)) {
                         ok = false;
                         break;
@@ -441,7 +644,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                         for (int k = 0; k < kKBlockBytes / 32; ++k) {
                             // advance both operands by 32 bytes of K inside the swizzled row
                             tc_mma<KIND>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                                         (kb > 0 || at > 0 || k > 0) ? 1u : 0u);
+                                         (kb > kb0 || at > 0 || k > 0) ? 1u : 0u);
                         }
                     }
                     tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
@@ -470,8 +673,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         int s = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < p.kblocks; ++kb) {
+        Segments segs(p, total_tiles);
+        int tile, kb0, kb1;
+        while (ok && segs.next(tile, kb0, kb1)) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 if (!mbar_wait(&rawfull[s], phase, s_abort, p.err_flag, 0x200)) {
                     ok = false;
                     break;
@@ -533,51 +738,147 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         int as = 0;
         uint32_t aphase = 0;
         const bool has_zero = p.zeros != nullptr;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        Segments segs(p, total_tiles);
+        int tile, kb0, kb1;
+        const int row = quad * 32 + lane;            // this thread's row of the tile = its TMEM lane
+        // dq and rowsum of a chunk's 16 batch rows, spread over the lanes (lane j: dq, lane 16 + j: rowsum)
+        auto load_rowfac = [&](int mt, int c0) -> float {
+            const int j = lane & 15, m = mt * p.Mb + c0 + j;
+            const bool want = c0 + j < p.Mb && m < p.M && (lane < 16 || has_zero);
+            return want ? (lane < 16 ? p.dq : p.rowsum)[m] : 0.0f;
+        };
+        while (segs.next(tile, kb0, kb1)) {
             const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            // Everything the epilogue needs besides the accumulator is requested before the wait for
+            // it, so these loads (a trip to L2 or HBM each) run under the tile's main loop.
+            const int n = nt * kTileN + row;
+            const bool n_ok = n < p.N;
+            float scale = 0.0f, zero = 0.0f, bias = 0.0f, fac = 0.0f;
+            if (kb0 == 0) {
+                scale = n_ok ? (p.scales ? __ldg(p.scales + n) : 1.0f) : 0.0f;
+                zero = (n_ok && has_zero) ? __ldg(p.zeros + n) : 0.0f;
+                bias = (n_ok && p.bias) ? p.bias[n] : 0.0f;
+                fac = load_rowfac(mt, chunk0);
+            }
             if (!mbar_wait(&tfull[as], aphase, s_abort, p.err_flag, 0x80)) break;
             tc_fence_after();
-            const int n = nt * kTileN + quad * 32 + lane;
-            const bool n_ok = n < p.N;
-            const float scale = n_ok ? (p.scales ? p.scales[n] : 1.0f) : 0.0f;
-            const float zero = (n_ok && has_zero) ? p.zeros[n] : 0.0f;
-            const float bias = (n_ok && p.bias) ? p.bias[n] : 0.0f;
             const uint32_t t_base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(as * BNt);
-            for (int c0 = chunk0; c0 < p.Mb; c0 += 16 * (kEpiWarps / 4)) {
-                uint32_t r[T][16];
+            if (kb0 > 0) {
+                // A later part of a tile's K range: leave the raw accumulators for the CTA that holds
+                // the tile's first K blocks ([column][row]: a warp stores 32 consecutive rows).
+                float *ws = p.sk_ws + (size_t)blockIdx.x * BNt * kTileN;
+                for (int c0 = chunk0; c0 < p.Mb; c0 += 16 * (kEpiWarps / 4)) {
 #pragma unroll
-                for (int t = 0; t < T; ++t) tmem_ld16(t_base + (uint32_t)(t * p.Mb + c0), r[t]);
-                tmem_ld_wait();
+                    for (int t = 0; t < T; ++t) {
+                        uint32_t x[16];
+                        tmem_ld16(t_base + (uint32_t)(t * p.Mb + c0), x);
+                        tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = mt * p.Mb + c0 + j;
-                    if (m >= p.M || c0 + j >= p.Mb) continue;
-                    float acc;
-                    if (T == 1)
-                        acc = __uint_as_float(r[0][j]);
-                    else if (KIND == KIND_I8)
-                        acc = ((float)(int)r[0][j] * 128.0f + (float)(int)r[1][j]) * p.acc_scale;
-                    else if (T == 3)
-                        acc = (__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) +
-                              __uint_as_float(r[T - 1][j]);
-                    else
-                        acc = __uint_as_float(r[0][j]) + __uint_as_float(r[T > 1 ? 1 : 0][j]);
-                    const float dot = acc * p.dq[m];
-                    const float v = finish_output_fast(dot, scale, zero, has_zero ? p.rowsum[m] : 0.0f,
-                                                       p.bias != nullptr, bias, p.epilogue);
-                    if (n_ok) {   // a warp writes 32 consecutive n
-                        if (p.ag.world == 0) {
-                            p.out[(size_t)m * p.N + n] = v;
-                        } else {   // plain peer stores over NVLink (and one local store)
-                            const size_t at = (size_t)m * p.ag.n_total + p.ag.col0 + n;
-                            for (int r = 0; r < p.ag.world; ++r) p.ag.peer_out[r][at] = v;
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < p.Mb) ws[(size_t)(t * p.Mb + c0 + j) * kTileN + row] = __uint_as_float(x[j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&tempty[as]);
+                    // this warp's part of the partial is stored: count it in (release); the finishing
+                    // CTA reads once all eight warps have
+                    __threadfence();
+                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sk_flags + blockIdx.x) : "memory");
+                }
+            } else {
+                // This CTA finishes the tile.  If its share ended before the tile's last K block, the next
+                // CTA(s) hold the rest: wait (bounded) for their partials and add them in CTA order.
+                const int others = (kb1 < p.kblocks) ? (p.kblocks - kb1 + p.sk_steps - 1) / p.sk_steps : 0;
+                bool partials_ok = true;
+                for (int o = 1; o <= others; ++o) {
+                    const unsigned *flag = p.sk_flags + blockIdx.x + o;
+                    const long long t0 = clock64();
+                    for (;;) {
+                        unsigned f;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
+                        if (f >= (unsigned)kEpiWarps) break;
+                        if (*s_abort || clock64() - t0 > kWaitCycles) {
+                            *s_abort = 1;
+                            atomicOr(p.err_flag, 0x800);
+                            partials_ok = false;
+                            break;
+                        }
+                    }
+                    if (!partials_ok) break;
+                }
+                for (int c0 = chunk0; c0 < p.Mb && partials_ok; c0 += 16 * (kEpiWarps / 4)) {
+                    uint32_t r[T][16];
+#pragma unroll
+                    for (int t = 0; t < T; ++t) tmem_ld16(t_base + (uint32_t)(t * p.Mb + c0), r[t]);
+                    const float fac_next = load_rowfac(mt, c0 + 16 * (kEpiWarps / 4));   // next chunk's
+                    tmem_ld_wait();
+                    for (int o = 1; o <= others; ++o) {
+                        const float *ws = p.sk_ws + (size_t)(blockIdx.x + o) * BNt * kTileN;
+#pragma unroll
+                        for (int t = 0; t < T; ++t)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (c0 + j >= p.Mb) continue;
+                                const uint32_t x = __float_as_uint(__ldcg(ws + (size_t)(t * p.Mb + c0 + j) * kTileN + row));
+                                r[t][j] = (KIND == KIND_I8)
+                                              ? (uint32_t)((int)r[t][j] + (int)x)
+                                              : __float_as_uint(__uint_as_float(r[t][j]) + __uint_as_float(x));
+                            }
+                    }
+                    // The 16 outputs are computed in straight-line code (one specialisation per
+                    // activation, no branch per output: with a branch per output the two warps a
+                    // scheduler has here ran them one after another at full instruction latency), then
+                    // stored under a predicate.
+                    float v[16];
+                    switch (p.epilogue) {
+                    case FNN_EPI_RELU:
+                        finish_chunk<KIND, T, FNN_EPI_RELU>(r, fac, scale, zero, bias, p.bias != nullptr, p.acc_scale, v);
+                        break;
+                    case FNN_EPI_GELU:
+                        finish_chunk<KIND, T, FNN_EPI_GELU>(r, fac, scale, zero, bias, p.bias != nullptr, p.acc_scale, v);
+                        break;
+                    case FNN_EPI_SILU:
+                        finish_chunk<KIND, T, FNN_EPI_SILU>(r, fac, scale, zero, bias, p.bias != nullptr, p.acc_scale, v);
+                        break;
+                    default:
+                        finish_chunk<KIND, T, FNN_EPI_NONE>(r, fac, scale, zero, bias, p.bias != nullptr, p.acc_scale, v);
+                        break;
+                    }
+                    const int m0 = mt * p.Mb + c0;
+                    const int jmax = n_ok ? min(16, min(p.Mb - c0, p.M - m0)) : 0;   // rows of this chunk that exist
+                    if (p.ag.world == 0) {   // a warp writes 32 consecutive n
+                        float *dst = p.out + (size_t)m0 * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < jmax) dst[(size_t)j * p.N] = v[j];
+                    } else {   // plain peer stores over NVLink (and one local store)
+                        const size_t at = (size_t)m0 * p.ag.n_total + p.ag.col0 + n;
+                        for (int rk = 0; rk < p.ag.world; ++rk) {
+                            float *dst = p.ag.peer_out[rk] + at;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (j < jmax) dst[(size_t)j * p.ag.n_total] = v[j];
+                        }
+                    }
+                    fac = fac_next;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[as]);
+                if (lane == 0) {
+                    // the last of the eight warps to have read a partial hands its counters back for the
+                    // next launch (nobody else touches them until then)
+                    for (int o = 1; o <= others; ++o) {
+                        unsigned *done = p.sk_flags + 1024 + blockIdx.x + o;
+                        if (atomicAdd(done, 1u) == (unsigned)kEpiWarps - 1u) {
+                            *done = 0u;
+                            p.sk_flags[blockIdx.x + o] = 0u;
                         }
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[as]);
             if (++as == 2) {
                 as = 0;
                 aphase ^= 1;
@@ -587,7 +888,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols)
                      : "memory");
@@ -703,6 +1004,18 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     const size_t bq_bytes = (size_t)T * Mpad * Kp;
     const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
     const size_t need = bq_al + (size_t)Mpad * 8 + 256;
+    // A layer with tiles for at most a quarter of the SMs (a narrow down-projection) is bound by the
+    // per-CTA rate of its long K loops: a 128-byte K block costs four MMA instructions of about 60
+    // cycles each however few batch columns they carry.  Such layers split their K loops over all
+    // SMs, and the partial accumulators of a split tile meet in a workspace behind the activation
+    // planes.  With more tiles the extra epilogues cost more than the idle SMs (measured).
+    const int n_tiles = (N + kTileN - 1) / kTileN;
+    const int kblocks = (Kbytes + kKBlockBytes * ATOMS - 1) / (kKBlockBytes * ATOMS);
+    const int sms = std::min(ctx->sm_count, 1024);
+    const int tiles = n_tiles * m_tiles;
+    const bool split_k = tiles * 4 <= sms && kblocks >= 8 && !fixed_scratch && ctx->sk_flags != nullptr;
+    const size_t ws_off = (need + 255) & ~(size_t)255;
+    const size_t ws_bytes = split_k ? (size_t)sms * T * Mb * kTileN * 4 : 0;
     int rc = FNN_OK;
     uint8_t *bq;
     if (fixed_scratch) {
@@ -712,7 +1025,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
                     M, K, need, fixed_bytes);
         bq = fixed_scratch;
     } else {
-        rc = ensure_scratch(ctx, need);
+        rc = ensure_scratch(ctx, ws_off + ws_bytes);
         if (rc != FNN_OK) return rc;
         bq = (uint8_t *)ctx->scratch;
     }
@@ -724,7 +1037,8 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
                        FNN_ERR_DISPATCH);
     // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
     // kernels makes every SM reconfigure (and drain) twice per call
-    auto prep = act_prep_kernel<KIND, T, WF == WF_I4>;
+    const bool regs_ok = K % 8 == 0 && K <= kPrepHold * 256 * 8 && (reinterpret_cast<uintptr_t>(a.a) & 15) == 0;
+    auto prep = regs_ok ? act_prep_regs_kernel<KIND, T, WF == WF_I4> : act_prep_kernel<KIND, T, WF == WF_I4>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(prep, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared),
                    FNN_ERR_DISPATCH);
@@ -752,7 +1066,6 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     } else {
         map_s = map_a;   // unused
     }
-
     TcParams p{};
     p.scales = (w->fmt == FNN_FMT_I4CB) ? nullptr : w->scales;  // block scales are folded into the operand
     p.zeros = w->zeros;
@@ -766,9 +1079,9 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     p.N = N;
     p.K = K;
     p.Mb = Mb;
-    p.n_tiles = (N + kTileN - 1) / kTileN;
+    p.n_tiles = n_tiles;
     p.m_tiles = m_tiles;
-    p.kblocks = (Kbytes + kKBlockBytes * ATOMS - 1) / (kKBlockBytes * ATOMS);
+    p.kblocks = kblocks;
     p.a_fmt = (w->fmt == FNN_FMT_F4) ? kFmtE2M1 : kFmtE4M3;
     p.acc_scale = (WF == WF_I4) ? 0.0625f : 1.0f;
     p.epilogue = a.epilogue;
@@ -780,7 +1093,14 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     stages = std::max(2, std::min(stages, 8));
     p.stages = stages;
     const size_t smem = 1024 + (size_t)stages * (a_bytes + b_stride + raw_bytes) + (3 * stages + 4) * 8 + 64 + 64;
-    const int grid = std::min(p.n_tiles * p.m_tiles, ctx->sm_count);
+    int grid = std::min(tiles, ctx->sm_count);
+    if (split_k) {
+        const long long steps = (long long)tiles * kblocks;
+        grid = (int)std::max<long long>(1, std::min<long long>(sms, steps / 4));   // at least four steps per CTA
+        p.sk_steps = (int)((steps + grid - 1) / grid);
+        p.sk_ws = (float *)(bq + ws_off);
+        p.sk_flags = ctx->sk_flags;
+    }
     const int threads = (2 + kEpiWarps + (WF == WF_TMA ? 0 : kXfWarps)) * 32;
     auto kern = qmm_tc_kernel<KIND, T, WF>;
     FNN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),

@@ -62,8 +62,9 @@ def test_noalloc_entry_matches_regular_entry_on_two_calls(backend, fmt):
             backend.synchronize()
             got = np.frombuffer(backend.read_arena(arena, out_off, m * n * 4), np.float32).reshape(m, n)
             ref = np.frombuffer(backend.read_arena(arena, ref_off, m * n * 4), np.float32).reshape(m, n)
-            # same kernel, same arithmetic: the two entry points agree to the bit
-            assert np.array_equal(got, ref)
+            # same kernel, same arithmetic; the regular entry point may split a tile's K range over
+            # several CTAs, which changes the order of the f32 additions only
+            assert max_err_vs_rms(got, ref) <= 1e-5
             want = orc.qmatmul(q, x, bias if use_bias else None, epi)
             assert max_err_vs_rms(got, want) <= 1e-2
     finally:
