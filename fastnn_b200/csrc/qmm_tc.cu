@@ -103,6 +103,11 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1),
+                 "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
                                             int c1, int c2) {
     asm volatile(
@@ -546,6 +551,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                 mbar_expect_tx(&full[i], full_tx);   // stage i: all stages start empty
                 load_w(i, nt, kb0 + i);
             }
+            // The activation planes may still be being written: an L2 prefetch of the first tile reads
+            // nothing into this SM, but it has the address translated before the copies that follow
+            // griddepcontrol.wait ask for it (L2 is the point of coherence, so nothing stale can result).
+            tma_prefetch_3d(&map_a, kb0 * ATOMS * kKBlockBytes, (tile % p.m_tiles) * p.Mb, 0);
         }
     }
     if (WF == WF_CB && threadIdx.x >= 64 && threadIdx.x < 80) s_cb[threadIdx.x - 64] = p.codebook[threadIdx.x - 64];
@@ -817,15 +826,20 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                     for (int o = 1; o <= others; ++o) {
                         const float *ws = p.sk_ws + (size_t)(blockIdx.x + o) * BNt * kTileN;
 #pragma unroll
-                        for (int t = 0; t < T; ++t)
+                        for (int t = 0; t < T; ++t) {
+                            // all 16 loads of a term in flight together (a warp reads 32 consecutive rows)
+                            uint32_t x[16];
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                if (c0 + j >= p.Mb) continue;
-                                const uint32_t x = __float_as_uint(__ldcg(ws + (size_t)(t * p.Mb + c0 + j) * kTileN + row));
+                            for (int j = 0; j < 16; ++j)
+                                x[j] = (c0 + j < p.Mb)
+                                           ? __float_as_uint(__ldcg(ws + (size_t)(t * p.Mb + c0 + j) * kTileN + row))
+                                           : 0u;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
                                 r[t][j] = (KIND == KIND_I8)
-                                              ? (uint32_t)((int)r[t][j] + (int)x)
-                                              : __float_as_uint(__uint_as_float(r[t][j]) + __uint_as_float(x));
-                            }
+                                              ? (uint32_t)((int)r[t][j] + (int)x[j])
+                                              : __float_as_uint(__uint_as_float(r[t][j]) + __uint_as_float(x[j]));
+                        }
                     }
                     // The 16 outputs are computed in straight-line code (one specialisation per
                     // activation, no branch per output: with a branch per output the two warps a
