@@ -202,14 +202,28 @@ __device__ __forceinline__ void split_terms(float x, uint8_t t[3]) {
     }
 }
 
+// The activations are written by the kernel before this one on the stream, so they may only be
+// read after griddepcontrol.wait.  A load through a `const __restrict__` pointer counts as invariant
+// for the compiler, which may then move it above the wait (it did: a chain of layers read the
+// previous run's activations).  The activation pointers of these kernels therefore carry no
+// __restrict__, and the unrolled loads of the register form are volatile asm, which keeps its place
+// after the (volatile asm) wait.
+__device__ __forceinline__ float4 ld_after_wait(const float4 *p) {
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
 // ---- activation rewrite ---------------------------------------------------------------------
 // One block per batch row.  Writes T byte planes Bq[t][m][Kp] (rows zero-padded to Kp), the
 // per-row factor dq[m] and the row sum.  PERM8: inside every group of eight k the bytes are stored
 // in the order 0,2,4,6,1,3,5,7 -- the order in which the I4 transform emits its weights.
 template <int KIND, int T, bool PERM8>
 __global__ void __launch_bounds__(256)
-act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
-                float *__restrict__ dq, float *__restrict__ rowsum) {
+act_prep_kernel(const float *act, int M, int K, int Kp, int Mpad, uint8_t *bq, float *dq, float *rowsum) {
     __shared__ float s_max[8], s_sum[8];
     // reads the activations and overwrites planes the previous tensor-core kernel may still read
     pdl_launch_dependents();
@@ -278,8 +292,7 @@ act_prep_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, u
 constexpr int kPrepHold = 8;   // units of eight elements a thread can hold
 template <int KIND, int T, bool PERM8>
 __global__ void __launch_bounds__(256)
-act_prep_regs_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mpad, uint8_t *__restrict__ bq,
-                     float *__restrict__ dq, float *__restrict__ rowsum) {
+act_prep_regs_kernel(const float *act, int M, int K, int Kp, int Mpad, uint8_t *bq, float *dq, float *rowsum) {
     __shared__ float s_max[8], s_sum[8];
     pdl_launch_dependents();
     pdl_wait();
@@ -292,8 +305,8 @@ act_prep_regs_kernel(const float *__restrict__ act, int M, int K, int Kp, int Mp
         const int u = tid + i * 256;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
         if (u < units) {
-            a = row4[2 * u];
-            b = row4[2 * u + 1];
+            a = ld_after_wait(row4 + 2 * u);
+            b = ld_after_wait(row4 + 2 * u + 1);
         }
         v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
         v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
