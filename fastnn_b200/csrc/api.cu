@@ -330,14 +330,18 @@ static int qmatmul_impl(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a, 
     QmmArgs args{w, a, out, bias, M, epilogue};
     switch (path) {
     case FNN_PATH_AUTO:
-        // Measured crossover: the fragment kernels win up to 10 batch rows everywhere, and up to 12 on
-        // layers with so few 128-row tiles that the tcgen05 kernel would leave half of the SMs idle (its
-        // two-launch sequence has a floor of about 17 us there); tcgen05 beyond.
+        // Measured crossover.  The 8-bit fragment kernel wins up to 8 batch rows (beyond that it runs
+        // 16-row groups at twice the time and the tcgen05 sequence, about 14.5 us at K=4096 N=11008, is
+        // ahead); FP8, which rides the fp16 fragment kernel, up to 4.  Layers with tiles for at most a
+        // quarter of the SMs keep the fragment kernels longer (12 and 8 rows): there the tcgen05
+        // kernel is bound by its fixed cost of about 18 us.
         {
             const bool frag_ok = qmm_mma_supported(w, M) && auto_uses_mma(w);
             const size_t tiles128 = div_ceil(w->N, (size_t)128);
-            const size_t frag_max = !frag_ok ? 0 : (tiles128 * 2 <= (size_t)ctx->sm_count ? 12 : 10);
-            if (qmm_tc_supported(w, M) && M > frag_max && M > 8) return launch_qmm_tc(ctx, args);
+            const bool narrow = tiles128 * 4 <= (size_t)ctx->sm_count;
+            const size_t frag_max =
+                !frag_ok ? 0 : (w->fmt == FNN_FMT_F8 ? (narrow ? 8 : 4) : (narrow ? 12 : 8));
+            if (qmm_tc_supported(w, M) && M > frag_max && M > 4) return launch_qmm_tc(ctx, args);
         }
         // tiny layers stay on the row kernel: a 16-row x 128-k fragment tile would be mostly padding
         if (qmm_mma_supported(w, M) && auto_uses_mma(w)) return launch_qmm_mma(ctx, args);

@@ -1058,10 +1058,8 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     }
     float *dq = (float *)(bq + bq_al);
     float *rowsum = dq + Mpad;
-    if (Mpad > M)  // padded batch rows of every term plane must read as zero
-        FNN_CUDA_CHECK(cudaMemset2DAsync(bq + (size_t)M * Kp, (size_t)Mpad * Kp, 0,
-                                         (size_t)(Mpad - M) * Kp, T, ctx->stream),
-                       FNN_ERR_DISPATCH);
+    // Batch rows M .. Mpad of the planes are never written: a batch row is one column of the MMA, so
+    // whatever those rows hold only reaches accumulator columns that the epilogue does not store.
     // same shared-memory carve-out as the main kernel: alternating carve-outs between consecutive
     // kernels makes every SM reconfigure (and drain) twice per call
     const bool regs_ok = K % 8 == 0 && K <= kPrepHold * 256 * 8 && (reinterpret_cast<uintptr_t>(a.a) & 15) == 0;
