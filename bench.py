@@ -809,7 +809,7 @@ def c5_chain(fnn, backend, rank, world, dist, layers=32, m=64, steps=3):
            "us_per_layer": round(us_layer, 2), "ms_per_step": round(ms / steps, 3),
            "weight_gbs_all_ranks": round(wbytes / (us_layer * 1e-6) / 1e9, 1),
            "tflops_all_ranks": round(flops / (us_layer * 1e-6) / 1e12, 2),
-           "launches_per_layer": launches_per_layer, "gathers_per_layer": 4,
+           "launches_per_layer": launches_per_layer, "gathers_per_layer": 4 if world > 1 else 0,
            "parity_err_layer0": err if err is None else float(f"{err:.3g}")}
     for l in lin:
         for v in l.values():

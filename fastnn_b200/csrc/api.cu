@@ -36,6 +36,62 @@ int ensure_scratch(fnn_cuda_ctx *ctx, size_t bytes) {
     return FNN_OK;
 }
 
+// Rows of `width` bytes from src (pitch spitch) to dst (pitch dpitch).  VEC bytes per thread and
+// access: 16 when every pointer, pitch and the width are multiples of 16, else 4, else 1.  A kernel
+// rather than a copy-engine node: inside a captured plan a memcpy node cannot overlap its
+// neighbours the way programmatic dependent launches do, and costs several microseconds.
+template <typename V>
+__global__ void copy2d_kernel(unsigned char *dst, size_t dpitch, const unsigned char *src, size_t spitch,
+                              size_t width_v, size_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = width_v * rows, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t r = i / width_v, c = i - r * width_v;
+        reinterpret_cast<V *>(dst + r * dpitch)[c] = reinterpret_cast<const V *>(src + r * spitch)[c];
+    }
+}
+
+// The common case of the element-wise instruction: operands as long as the output (no broadcast),
+// 16-byte aligned, four elements per thread and access.
+__global__ void elementwise_vec_kernel(int op, const float4 *a, const float4 *b, float4 *out, size_t n4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int base = op & 0xFF, act = op >> 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 x = a[i];
+        float4 y = x;
+        if (base == FNN_EW_ADD || base == FNN_EW_MUL || base == FNN_EW_SUB) y = b[i];
+        float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w}, r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            switch (base) {
+            case FNN_EW_ADD:
+                r[j] = __fadd_rn(xs[j], ys[j]);
+                break;
+            case FNN_EW_MUL:
+                r[j] = __fmul_rn(xs[j], ys[j]);
+                break;
+            case FNN_EW_SUB:
+                r[j] = __fsub_rn(xs[j], ys[j]);
+                break;
+            case FNN_EW_RELU:
+                r[j] = apply_act(xs[j], FNN_EPI_RELU);
+                break;
+            case FNN_EW_GELU:
+                r[j] = apply_act(xs[j], FNN_EPI_GELU);
+                break;
+            default:
+                r[j] = apply_act(xs[j], FNN_EPI_SILU);
+                break;
+            }
+            if (act) r[j] = apply_act(r[j], act);
+        }
+        out[i] = make_float4(r[0], r[1], r[2], r[3]);
+    }
+}
+
 // out[i] = op(a[i % a_len], b[i % b_len]); unary ops read a only.
 __global__ void elementwise_kernel(int op, const float *a, size_t a_len, const float *b,
                                    size_t b_len, float *out, size_t out_len) {
@@ -547,9 +603,40 @@ int fnn_cuda_elementwise(fnn_cuda_ctx *ctx, int op, fnn_cuda_arena *arena, size_
     const float *a = (const float *)(arena->base + a_offset);
     const float *b = binary ? (const float *)(arena->base + b_offset) : a;
     float *o = (float *)(arena->base + out_offset);
-    FNN_CUDA_CHECK(launch_pdl(elementwise_kernel, grid_for(ctx, out_len, 256), 256, 0, ctx, op, a,
-                              a_len, b, binary ? b_len : (size_t)1, o, out_len),
-                   FNN_ERR_DISPATCH);
+    const bool same_len = a_len == out_len && (!binary || b_len == out_len);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                           reinterpret_cast<uintptr_t>(o)) & 15u) == 0;
+    if (same_len && aligned && out_len % 4 == 0) {
+        FNN_CUDA_CHECK(launch_pdl(elementwise_vec_kernel, grid_for(ctx, out_len / 4, 256), 256, 0, ctx, op,
+                                  reinterpret_cast<const float4 *>(a), reinterpret_cast<const float4 *>(b),
+                                  reinterpret_cast<float4 *>(o), out_len / 4),
+                       FNN_ERR_DISPATCH);
+    } else {
+        FNN_CUDA_CHECK(launch_pdl(elementwise_kernel, grid_for(ctx, out_len, 256), 256, 0, ctx, op, a,
+                                  a_len, b, binary ? b_len : (size_t)1, o, out_len),
+                       FNN_ERR_DISPATCH);
+    }
+    ctx->launches++;
+    return FNN_OK;
+}
+
+// Device-to-device copy of `rows` rows of `width` bytes as a kernel on the context's stream.
+static int launch_copy2d(fnn_cuda_ctx *ctx, unsigned char *dst, size_t dpitch, const unsigned char *src,
+                         size_t spitch, size_t width, size_t rows) {
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | dpitch | spitch | width;
+    if ((bits & 15u) == 0) {
+        FNN_CUDA_CHECK(launch_pdl(copy2d_kernel<uint4>, grid_for(ctx, width / 16 * rows, 256), 256, 0, ctx, dst,
+                                  dpitch, src, spitch, width / 16, rows),
+                       FNN_ERR_DISPATCH);
+    } else if ((bits & 3u) == 0) {
+        FNN_CUDA_CHECK(launch_pdl(copy2d_kernel<uint32_t>, grid_for(ctx, width / 4 * rows, 256), 256, 0, ctx, dst,
+                                  dpitch, src, spitch, width / 4, rows),
+                       FNN_ERR_DISPATCH);
+    } else {
+        FNN_CUDA_CHECK(launch_pdl(copy2d_kernel<unsigned char>, grid_for(ctx, width * rows, 256), 256, 0, ctx, dst,
+                                  dpitch, src, spitch, width, rows),
+                       FNN_ERR_DISPATCH);
+    }
     ctx->launches++;
     return FNN_OK;
 }
@@ -561,10 +648,7 @@ int fnn_cuda_memcpy(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset,
     FNN_REQUIRE(span_ok(arena, dst_offset, bytes) && span_ok(arena, src_offset, bytes),
                 FNN_ERR_DISPATCH, "memcpy: slice outside arena");
     if (bytes == 0) return FNN_OK;
-    FNN_CUDA_CHECK(cudaMemcpyAsync(arena->base + dst_offset, arena->base + src_offset, bytes,
-                                   cudaMemcpyDeviceToDevice, ctx->stream),
-                   FNN_ERR_DISPATCH);
-    return FNN_OK;
+    return launch_copy2d(ctx, arena->base + dst_offset, bytes, arena->base + src_offset, bytes, bytes, 1);
 }
 
 int fnn_cuda_memcpy2d(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offset, size_t dst_pitch,
@@ -576,10 +660,8 @@ int fnn_cuda_memcpy2d(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t dst_offse
                     span_ok(arena, dst_offset, (rows - 1) * dst_pitch + width) &&
                     span_ok(arena, src_offset, (rows - 1) * src_pitch + width),
                 FNN_ERR_DISPATCH, "memcpy2d: rows outside arena or wider than their pitch");
-    FNN_CUDA_CHECK(cudaMemcpy2DAsync(arena->base + dst_offset, dst_pitch, arena->base + src_offset, src_pitch,
-                                     width, rows, cudaMemcpyDeviceToDevice, ctx->stream),
-                   FNN_ERR_DISPATCH);
-    return FNN_OK;
+    return launch_copy2d(ctx, arena->base + dst_offset, dst_pitch, arena->base + src_offset, src_pitch, width,
+                         rows);
 }
 
 int fnn_cuda_fill(fnn_cuda_ctx *ctx, fnn_cuda_arena *arena, size_t offset, size_t bytes,

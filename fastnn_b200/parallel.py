@@ -142,6 +142,11 @@ class AllGatherLinear:
 
     def forward(self, a_dev_ptr: int, m: int) -> None:
         lib, b = self.backend.lib, self.backend
+        if self.world == 1:   # nothing to gather: the plain call writes the rows where they belong
+            _check_rc(lib.fnn_cuda_qmatmul_ptr(b.ctx, self.weight.handle, a_dev_ptr,
+                                               self.pa.device_ptr + self.out_off, self.bias_ptr, m,
+                                               self.epilogue, L.PATH_AUTO))
+            return
         _check_rc(lib.fnn_cuda_qmatmul_allgather(
             b.ctx, self.weight.handle, a_dev_ptr, self.bias_ptr, m, self.epilogue, self.rank, self.world,
             self.pa.peers, self.out_off, self.ctr_off, self.n, self.col0))
