@@ -493,8 +493,9 @@ def run_ours(args):
 # captures of `python bench.py --only <point> --only-m <M>`; `source` names the kernel and the date
 # of the capture.  A point without an entry reports null.
 NCU_TRAFFIC = {
-    ("i8", 4096, 11008, 1): {"bytes": 45233920,
-                             "source": "qmm_mma8_kernel, ncu --set full, 2026-11-25: 45.2326 MB read + 1.3 KB written"},
+    ("i8", 4096, 11008, 1): {"bytes": 45234432,
+                             "source": "qmm_mma8_kernel (444 blocks of 256 threads), ncu --set full: 45.231872 MB read + 2.56 KB "
+                                       "written per launch (profiles/qmm_mma8_i8_m1_config2.md)"},
 }
 
 

@@ -66,7 +66,6 @@ SIGNATURES = {
                                        _sz]),
     "fnn_cuda_qmatmul_allgather": (_int, [_vp, _vp, _vp, _vp, _sz, _int, _int, _int, _c.POINTER(_vp), _sz, _sz,
                                           _sz, _sz]),
-    "fnn_cuda_allgather_wait": (_int, [_vp, _vp, _sz, _int]),
     "fnn_cuda_elementwise": (_int, [_vp, _int, _vp, _sz, _sz, _sz, _sz, _sz, _sz]),
     "fnn_cuda_rms_norm": (_int, [_vp, _vp, _sz, _sz, _c.c_longlong, _sz, _sz, _c.c_float, _sz]),
     "fnn_cuda_row_norm": (_int, [_vp, _vp, _int, _sz, _sz, _c.c_longlong, _c.c_longlong, _sz, _c.c_longlong, _sz,

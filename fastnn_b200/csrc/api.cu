@@ -542,18 +542,12 @@ int fnn_cuda_qmatmul_allgather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const flo
         g.peer_arrive[r] = (unsigned *)((uint8_t *)peer_bases[r] + counter_offset);
     }
     g.ticket = ctx->err_flag + 1;
+    g.rank = rank;
     g.world = world;
     g.n_total = (int)n_total;
     g.col0 = (int)col0;
     QmmArgs args{w, a_dev, nullptr, bias_dev, M, epilogue, nullptr, &g};
     return launch_qmm_tc(ctx, args);
-}
-
-int fnn_cuda_allgather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t counter_offset, int world) {
-    clear_error();
-    FNN_REQUIRE(ctx && my_base && world >= 1 && world <= 8 && (counter_offset & 7u) == 0, FNN_ERR_DISPATCH,
-                "allgather_wait: bad argument");
-    return launch_allgather_wait(ctx, (unsigned *)((uint8_t *)my_base + counter_offset), world);
 }
 
 int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset, size_t counter_offset,

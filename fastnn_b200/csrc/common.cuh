@@ -341,8 +341,9 @@ __device__ __forceinline__ void gather_finish(const GatherArgs &g, unsigned step
 // CTA is done, adds one to every rank's arrival counter (release at system scope).
 struct AllGatherArgs {
     float *peer_out[8];          // every rank's [M, n_total] output
-    unsigned *peer_arrive[8];    // every rank's arrival counter
-    int *ticket;                 // local: CTAs of this launch that have finished
+    unsigned *peer_arrive[8];    // every rank's {arrivals, consumed} pair (one arrival per rank and launch)
+    int *ticket;                 // local: CTAs of this launch that have stored their outputs
+    int rank;
     int world, n_total, col0;
 };
 
@@ -365,7 +366,6 @@ bool qmm_mma8_supported(const fnn_cuda_qweight *w, size_t M);
 int launch_qmm_mma8(fnn_cuda_ctx *ctx, const QmmArgs &args);
 int launch_gather_wait(fnn_cuda_ctx *ctx, const unsigned long long *my_words, const unsigned *counters,
                        int world, int n_stride, float *out);
-int launch_allgather_wait(fnn_cuda_ctx *ctx, unsigned *counters, int world);
 int prepare_qmm_tc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w);
 // shapes automatic dispatch sends to the skinny tensor-core kernel
 static inline bool auto_uses_mma(const fnn_cuda_qweight *w) { return w->K >= 512 && w->N >= 64; }

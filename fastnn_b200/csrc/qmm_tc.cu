@@ -921,38 +921,37 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                      : "memory");
     }
     if (p.ag.world > 0 && threadIdx.x == 32) {
-        // Every store of this CTA happened before the barrier above; the fence makes them visible
-        // system-wide before the ticket.  The last CTA of the launch then tells every rank that this
-        // rank's block has arrived: fence (it has seen every other CTA's ticket), then one release add
-        // per rank.
-        __threadfence_system();
+        // Every store of this CTA happened before the barrier above.  A device-scope fence and a ticket
+        // hand them to the CTA that leaves last on this rank; that one CTA makes everything visible
+        // system-wide (one system-scope fence per launch: 148 of them at once cost about 10 us) and
+        // adds one arrival to every rank's counter (release).  It then waits (bounded) until every
+        // rank's arrival for this step is in before the kernel ends, so whatever follows on the
+        // stream reads complete rows without a separate consumer kernel.  counters = {arrivals,
+        // consumed} live in device memory and only grow: a captured graph can be replayed.
+        __threadfence();
         const int ticket = atomicAdd(p.ag.ticket, 1);
         if (ticket == (int)gridDim.x - 1) {
             *p.ag.ticket = 0;
             __threadfence_system();
             for (int r = 0; r < p.ag.world; ++r)
                 asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.ag.peer_arrive[r]) : "memory");
+            unsigned *counters = p.ag.peer_arrive[p.ag.rank];
+            const unsigned want = counters[1] + (unsigned)p.ag.world;
+            const long long t0 = clock64();
+            for (;;) {
+                unsigned got;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(counters) : "memory");
+                if ((int)(got - want) >= 0) {
+                    counters[1] = want;
+                    break;
+                }
+                if (clock64() - t0 > kWaitCycles) {   // gives up without consuming
+                    atomicOr(p.err_flag, 0x400);
+                    break;
+                }
+            }
         }
     }
-}
-
-// Consumer side of the fused GEMM + all-gather: counters = {arrivals, consumed}.  Waits (bounded) until
-// `world` more arrivals than have been consumed are in, then advances `consumed`; both live in device
-// memory, so a captured graph can be replayed.
-__global__ void allgather_wait_kernel(unsigned *counters, int world, int *err_flag) {
-    if (threadIdx.x != 0) return;
-    const unsigned want = counters[1] + (unsigned)world;
-    const long long t0 = clock64();
-    for (;;) {
-        unsigned got;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(counters) : "memory");
-        if ((int)(got - want) >= 0) break;
-        if (clock64() - t0 > kWaitCycles) {
-            atomicOr(err_flag, 0x400);
-            return;   // gives up without consuming: the next wait sees the same state
-        }
-    }
-    counters[1] = want;
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -1031,16 +1030,30 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     const size_t bq_bytes = (size_t)T * Mpad * Kp;
     const size_t bq_al = (bq_bytes + 255) & ~(size_t)255;
     const size_t need = bq_al + (size_t)Mpad * 8 + 256;
-    // A layer with tiles for at most a quarter of the SMs (a narrow down-projection) is bound by the
-    // per-CTA rate of its long K loops: a 128-byte K block costs four MMA instructions of about 60
-    // cycles each however few batch columns they carry.  Such layers split their K loops over all
-    // SMs, and the partial accumulators of a split tile meet in a workspace behind the activation
-    // planes.  With more tiles the extra epilogues cost more than the idle SMs (measured).
+    // A layer with few tiles and long K loops is bound by the per-CTA rate of those loops: a 128-byte
+    // K block costs four MMA instructions of about 60 cycles each however few batch columns they
+    // carry.  Such layers split every tile's K loop into `parts` shares on different SMs; the partial
+    // accumulators of a tile meet in a workspace behind the activation planes and the CTA with the
+    // first share adds them up.  `parts` comes from measured costs: a pipeline step of one CTA (0.35
+    // us; 0.8 with two atoms per step), an extra partial for the finishing CTA to read (1 us per 128
+    // accumulator columns) and about 3 us for the hand-over; shares shorter than that buy nothing.
     const int n_tiles = (N + kTileN - 1) / kTileN;
     const int kblocks = (Kbytes + kKBlockBytes * ATOMS - 1) / (kKBlockBytes * ATOMS);
     const int sms = std::min(ctx->sm_count, 1024);
     const int tiles = n_tiles * m_tiles;
-    const bool split_k = tiles * 4 <= sms && kblocks >= 8 && !fixed_scratch && ctx->sk_flags != nullptr;
+    int parts = 1;
+    if (!fixed_scratch && ctx->sk_flags != nullptr) {
+        const double t_step = ATOMS == 2 ? 0.8 : 0.35, c_part = 0.5 + (double)(T * Mb) / 128.0;
+        double best = 3.0;   // microseconds a split has to save before it is worth the hand-over
+        for (int q = 2; q <= std::min(sms / std::max(tiles, 1), 12); ++q) {
+            const double gain = kblocks * t_step * (1.0 - 1.0 / q) - c_part * (q - 1) - 3.0;
+            if (gain > best) {
+                best = gain;
+                parts = q;
+            }
+        }
+    }
+    const bool split_k = parts > 1;
     const size_t ws_off = (need + 255) & ~(size_t)255;
     const size_t ws_bytes = split_k ? (size_t)sms * T * Mb * kTileN * 4 : 0;
     int rc = FNN_OK;
@@ -1121,8 +1134,8 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     int grid = std::min(tiles, ctx->sm_count);
     if (split_k) {
         const long long steps = (long long)tiles * kblocks;
-        grid = (int)std::max<long long>(1, std::min<long long>(sms, steps / 4));   // at least four steps per CTA
-        p.sk_steps = (int)((steps + grid - 1) / grid);
+        p.sk_steps = (kblocks + parts - 1) / parts;
+        grid = (int)std::min<long long>(sms, (steps + p.sk_steps - 1) / p.sk_steps);
         p.sk_ws = (float *)(bq + ws_off);
         p.sk_flags = ctx->sk_flags;
     }
@@ -1169,13 +1182,6 @@ int dispatch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed, size_t fixe
         return launch_tc<KIND_F16, 1, WF_CB>(ctx, a, fixed, fixed_bytes);
     }
     return set_error(FNN_ERR_UNSUPPORTED, "qmatmul: tcgen05 path does not cover format %d", a.w->fmt);
-}
-
-int launch_allgather_wait(fnn_cuda_ctx *ctx, unsigned *counters, int world) {
-    allgather_wait_kernel<<<1, 32, 0, ctx->stream>>>(counters, world, ctx->err_flag);
-    FNN_CUDA_CHECK(cudaGetLastError(), FNN_ERR_DISPATCH);
-    ctx->launches++;
-    return FNN_OK;
 }
 
 int launch_qmm_tc(fnn_cuda_ctx *ctx, const QmmArgs &a) {

@@ -117,8 +117,8 @@ class PeerArena:
 class AllGatherLinear:
     """Column shard of a quantized Linear for any batch size: the tcgen05 kernel's epilogue stores
     this rank's [M, n_local] block into its column range of every rank's [M, N] rows over NVLink
-    (`fnn_cuda_qmatmul_allgather`), and `forward` ends with the consumer-side wait, so the rows at
-    `out_off` of the local arena are the next layer's activations.  Shards are equal (N divisible by
+    (`fnn_cuda_qmatmul_allgather`); the kernel ends only when every rank's block has arrived, so the
+    rows at `out_off` of the local arena are the next layer's activations.  Shards are equal (N divisible by
     the number of ranks).  `out_off` / `ctr_off`: offsets inside the PeerArena of the f32 [m_max, N]
     rows and of the 8-byte counter pair; the same on every rank."""
 
@@ -150,7 +150,6 @@ class AllGatherLinear:
         _check_rc(lib.fnn_cuda_qmatmul_allgather(
             b.ctx, self.weight.handle, a_dev_ptr, self.bias_ptr, m, self.epilogue, self.rank, self.world,
             self.pa.peers, self.out_off, self.ctr_off, self.n, self.col0))
-        _check_rc(lib.fnn_cuda_allgather_wait(b.ctx, self.pa.device_ptr, self.ctr_off, self.world))
 
     def close(self) -> None:
         self.weight.close()

@@ -235,21 +235,20 @@ int fnn_cuda_gather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t gather_offset,
  *   [out_offset]      f32 [M][n_total]   the gathered rows, ready to be the next layer's activations
  *   [counter_offset]  u32 arrivals | u32 consumed                       (8 bytes, zero at start)
  * The epilogue stores this rank's [M, n_local] block into columns [col0, col0 + n_local) of every
- * rank's rows with plain peer stores over NVLink; when the last CTA of the launch is done it fences
- * at system scope and adds one to every rank's `arrivals` (release).  fnn_cuda_allgather_wait
- * enqueues the consumer: it waits (bounded, about a second; on expiry the context's error flag is
- * raised and nothing is consumed) until `world` arrivals beyond `consumed` are in and then advances
- * `consumed`, so whatever follows it on the stream reads complete rows.  The counters only grow and
- * live in device memory: a captured graph of such steps can be replayed.  A buffer may be reused by
- * a later step once every rank has consumed it, which a chain of at least two gathered layers
- * guarantees (a rank can only start the step after next when its peers' later layers have
- * arrived).  Every rank must make the same sequence of calls.  Serves what the tcgen05 kernel
- * serves (K >= 128). */
+ * rank's rows with plain peer stores over NVLink.  The CTA that leaves last on a rank fences at
+ * system scope, adds one to every rank's `arrivals` (release) and then waits (bounded, about a
+ * second; on expiry the context's error flag is raised and nothing is consumed) until `world`
+ * arrivals beyond `consumed` are in, and advances
+ * `consumed`: when the call's kernel has finished, the rows are complete, and whatever follows it
+ * on the stream may read them.  The counters only grow and live in device memory: a captured graph
+ * of such steps can be replayed.  A buffer may be reused by a later step once every rank has read it,
+ * which a chain of at least two gathered layers guarantees (a rank can only finish the step after
+ * next when its peers have started theirs).  Every rank must make the same sequence of calls, each
+ * rank on its own GPU.  Serves what the tcgen05 kernel serves (K >= 128). */
 int fnn_cuda_qmatmul_allgather(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
                                const float *bias_dev, size_t M, int epilogue, int rank, int world,
                                void *const *peer_bases, size_t out_offset, size_t counter_offset,
                                size_t n_total, size_t col0);
-int fnn_cuda_allgather_wait(fnn_cuda_ctx *ctx, void *my_base, size_t counter_offset, int world);
 
 /* ---- remaining plan instructions ---------------------------------------------------
  * Binary ops broadcast by modulo, out[i] = op(a[i % a_len], b[i % b_len])
