@@ -972,6 +972,15 @@ class AotExecutor:
         self.plan, self.memory_plan, self.graph = self.executor.compile_with_weight_dtype(
             graph, weight_dtype)
 
+    @classmethod
+    def from_onnx(cls, source, quantize=None, backend=None,
+                  input_shapes: Optional[Dict[str, Sequence[int]]] = None) -> "AotExecutor":
+        """Compile an ONNX file (a path or its bytes) -- what fastnn's Python front end does with
+        `import_onnx_to_compute_graph` before it builds an `AotExecutor` (fastnn/io/onnx.py:276-466)."""
+        from .onnx_import import read_onnx, to_aot_arguments
+        nodes, params, ins, outs, shapes = to_aot_arguments(read_onnx(source), input_shapes)
+        return cls(nodes, params, ins, outs, shapes, quantize=quantize, backend=backend)
+
     def forward(self, inputs: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
         data = []
         for name in self.input_names:

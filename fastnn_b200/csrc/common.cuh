@@ -329,8 +329,15 @@ __device__ __forceinline__ void gather_finish(const GatherArgs &g, unsigned step
         const int ticket = atomicAdd(g.done_ctr, 1);
         if (ticket == (int)gridDim.x - 1) {
             *g.done_ctr = 0;
-            *g.last_m = M;
-            *g.step_ctr = step;
+            // A launch whose check of the previous step gave up advances nothing: the host sees the
+            // error at its next fnn_cuda_sync and has to zero the gather buffers on every rank before
+            // it uses them again (words of this step may have been published in part).
+            int failed;
+            asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(failed) : "l"(g.err_flag) : "memory");
+            if (!(failed & 0x100)) {
+                *g.last_m = M;
+                *g.step_ctr = step;
+            }
         }
     }
 }

@@ -217,10 +217,13 @@ const char *fnn_cuda_last_path(fnn_cuda_ctx *ctx);
  * proves that every peer is done reading the slot it is about to overwrite), and
  * fnn_cuda_gather_wait does the same for the last step and, when out_dev is given, writes the values
  * there as plain f32 [world][M][n_stride] for any other consumer.  Polls are bounded (about one
- * second): if a word never arrives the context's error flag is raised and fnn_cuda_sync reports it.
- * Every rank must make the same sequence of calls.  Serves all five formats with 1..4 batch rows (the
- * HBM-bound case where a separate collective costs more than the GEMV); gather larger batches with a
- * collective. */
+ * second, so ranks whose launches drift further apart than that report it too): if a word never
+ * arrives the context's error flag is raised, that launch does not advance the step counter, and
+ * fnn_cuda_sync reports it; words of the failed step may have been published in part, so the gather
+ * buffers and counters have to be zeroed on every rank before they are used again.  Every rank must
+ * make the same sequence of calls with the same n_stride (the check of the previous step indexes
+ * with it).  Serves all five formats with 1..4 batch rows (the HBM-bound case where a separate
+ * collective costs more than the GEMV); larger batches use fnn_cuda_qmatmul_allgather below. */
 int fnn_cuda_ipc_export(fnn_cuda_arena *arena, void *handle64);
 int fnn_cuda_ipc_open(fnn_cuda_ctx *ctx, const void *handle64, void **device_ptr);
 int fnn_cuda_ipc_close(fnn_cuda_ctx *ctx, void *device_ptr);

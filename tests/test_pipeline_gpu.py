@@ -162,3 +162,30 @@ def test_saved_plan_runs_through_runtime_without_requantizing(backend, tmp_path,
             assert np.array_equal(got, want)
     finally:
         rt.close()
+
+
+@pytest.mark.parametrize("quantize,fmt", [(8, orc.FMT_I8), ("f8", orc.FMT_F8)])
+def test_onnx_file_with_torch_style_linear_layers(backend, quantize, fmt, tmp_path):
+    """An ONNX file as PyTorch exports an MLP block -- Gemm(transB=1) + bias, SiLU as Sigmoid x Mul,
+    a second Gemm, symbolic batch -- through `AotExecutor.from_onnx`: both weights land on the
+    quantized MatMul with the epilogue fused, and the result follows the oracle."""
+    import onnx_wire as ow
+    k, h, n, m = 256, 512, 192, 5
+    w1, b1 = normal(60, (h, k), 0.05), normal(61, (h,), 0.01)       # torch layout [out, in]
+    w2, b2 = normal(62, (n, h), 0.05), normal(63, (n,), 0.01)
+    nodes = [ow.node("Gemm", ["x", "fc1.weight", "fc1.bias"], ["h1"], "fc1", transB=1),
+             ow.node("Sigmoid", ["h1"], ["s1"]), ow.node("Mul", ["h1", "s1"], ["a1"]),
+             ow.node("Gemm", ["a1", "fc2.weight", "fc2.bias"], ["y"], "fc2", transB=1, alpha=1.0, beta=1.0)]
+    path = tmp_path / "mlp.onnx"
+    path.write_bytes(ow.model(nodes, {"fc1.weight": w1, "fc1.bias": b1, "fc2.weight": w2, "fc2.bias": b2},
+                              [("x", ["batch", k])], ["y"], initializers_as_inputs=True))
+    aot = fnn.AotExecutor.from_onnx(str(path), quantize=quantize, backend=backend)
+    names = [i.kernel_name for i in aot.plan.instructions if isinstance(i, fnn.CallKernel)]
+    assert [nm for nm in names if nm.startswith("matmul_")] == ["matmul_" + ("i8" if quantize == 8 else "f8")] * 2, names
+    assert "silu_f32" not in names and "sigmoid_f32" not in names, names     # the activation is fused
+    x = normal(64, (m, k), 1.0)
+    got = aot.forward({"x": x})["y"]
+    q1, q2 = orc.quantize_kn(fmt, np.ascontiguousarray(w1.T)), orc.quantize_kn(fmt, np.ascontiguousarray(w2.T))
+    want = orc.qmatmul(q2, orc.qmatmul(q1, x, b1, orc.EPI_SILU), b2, orc.EPI_NONE)
+    assert got.shape == (m, n)
+    assert max_err_vs_rms(got, want) <= 1e-3
