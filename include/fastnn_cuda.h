@@ -50,7 +50,7 @@ enum {
     FNN_PATH_AUTO = 0,
     FNN_PATH_ROWS = 1, /* f32 CUDA-core row kernel (any shape)                */
     FNN_PATH_MMA = 2,  /* skinny-M tensor-core kernel, fragment-major weights  */
-    FNN_PATH_TC = 3    /* tcgen05 / TMEM / TMA GEMM for large M                */
+    FNN_PATH_TC = 3    /* tcgen05 / TMEM / TMA GEMM (5 batch rows and more)    */
 };
 
 /* Elementwise kernels of the plan ("add_f32", "mul_f32", "relu_f32", ...;
@@ -194,7 +194,8 @@ int fnn_cuda_qmatmul_ptr(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_
  * All five formats are served where the tcgen05 kernel is (K >= 128; the codebook format: K a
  * multiple of 128).  The first call on a device looks up the scratch array's device
  * address; make that call before any stream capture.  All calls share the array and it keeps
- * the previous call's contents (the kernel clears what has to start at zero itself), so two
+ * the previous call's contents (stale batch rows beyond M only reach accumulator columns that are
+ * never stored), so two
  * calls that overlap on the GPU -- different streams or contexts of one device -- race. */
 int fnn_cuda_qmatmul_noalloc(fnn_cuda_ctx *ctx, fnn_cuda_qweight *w, const float *a_dev,
                              float *out_dev, const float *bias_dev, size_t M, int epilogue);
