@@ -1053,7 +1053,19 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
             }
         }
     }
-    const bool split_k = parts > 1;
+    // More tiles than SMs, and a last wave that leaves many of them idle (224 tiles on 148 SMs): at
+    // medium batch every CTA takes an equal share of all steps instead of whole tiles; a share then
+    // starts and ends inside a tile, so a CTA hands over or adds at most one partial at either end.
+    int even_steps = 0;
+    if (parts == 1 && !fixed_scratch && ctx->sk_flags != nullptr && tiles > sms && T * Mb <= 128) {
+        const double t_step = ATOMS == 2 ? 0.8 : 0.35, c_part = 0.5 + (double)(T * Mb) / 128.0;
+        const long long steps = (long long)tiles * kblocks;
+        const long long share = (steps + sms - 1) / sms;
+        const double whole = (double)((tiles + sms - 1) / sms) * kblocks * t_step;
+        const double even = (double)share * t_step + 2.0 * c_part + 3.0;
+        if (whole - even > 3.0 && share >= 16) even_steps = (int)share;
+    }
+    const bool split_k = parts > 1 || even_steps > 0;
     const size_t ws_off = (need + 255) & ~(size_t)255;
     const size_t ws_bytes = split_k ? (size_t)sms * T * Mb * kTileN * 4 : 0;
     int rc = FNN_OK;
@@ -1134,7 +1146,7 @@ int launch_tc(fnn_cuda_ctx *ctx, const QmmArgs &a, uint8_t *fixed_scratch = null
     int grid = std::min(tiles, ctx->sm_count);
     if (split_k) {
         const long long steps = (long long)tiles * kblocks;
-        p.sk_steps = (kblocks + parts - 1) / parts;
+        p.sk_steps = even_steps > 0 ? even_steps : (kblocks + parts - 1) / parts;
         grid = (int)std::min<long long>(sms, (steps + p.sk_steps - 1) / p.sk_steps);
         p.sk_ws = (float *)(bq + ws_off);
         p.sk_flags = ctx->sk_flags;
