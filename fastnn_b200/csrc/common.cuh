@@ -66,6 +66,7 @@ struct fnn_cuda_ctx {
     std::vector<void *> retired_scratch;   // outgrown scratch buffers (captured graphs may still name them)
     int *err_flag = nullptr;  // device flag written by bounded waits that gave up; err_flag[1]: CTA ticket of
                               // the fused GEMM + all-gather
+    int *err_host = nullptr;  // pinned host copy of err_flag[0], refreshed by fnn_cuda_sync
     bool overlap_launches = true;   // programmatic dependent launch (fnn_cuda_ctx_set_overlap)
     unsigned *sk_flags = nullptr;   // 2 x 1024 zeroed counters of the tcgen05 kernel's split-K hand-over
 };
