@@ -235,6 +235,12 @@ qmm_mma8_kernel(P8 p) {
 
     const bool vec_ok = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15u) == 0);
     const int Kpad = p.KB * KBLK;
+    // groups of eight activations a thread keeps (single row, K <= 4096 per group of warps in the
+    // block); three-group blocks have no registers to spare for it
+    constexpr bool kCanHold = !MULTI && kG8 <= 2;
+    constexpr int kHeld = 2;
+    float hv[kCanHold ? kHeld : 1][8];
+    bool held = false;
     for (int k0 = 0; k0 < Kpad; k0 += p.Kc) {
         const int kc_len = min(p.Kc, Kpad - k0);
         const int KBc = kc_len / KBLK;
@@ -276,7 +282,52 @@ qmm_mma8_kernel(P8 p) {
             pdl_wait();
             if (p.gather_on) gc = gather_begin(p.g, blockIdx.x * NT + tid);
             // ---- per-row step and sum: max |a| over the whole row first ---------------------
-            frag::scan_rows<NT, MULTI ? 4 : 1>(p.act, p.M, p.K, vec_ok, s_part, s_mx, s_rs);
+            if (kCanHold && vec_ok && p.K % 8 == 0 && p.K <= NT * 8 * kHeld && kc_len >= Kpad) {
+                // A single batch row that is staged in one pass: every thread keeps its groups of eight
+                // consecutive activations in registers between the scan and the rewrite, so the row is
+                // read once.
+                held = true;
+                float mx = 0.0f, sum = 0.0f;
+#pragma unroll
+                for (int j = 0; j < kHeld; ++j) {
+                    const int g8 = tid + j * NT;
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                    if (g8 * 8 < p.K) {
+                        a = __ldg(reinterpret_cast<const float4 *>(p.act) + 2 * g8);
+                        b = __ldg(reinterpret_cast<const float4 *>(p.act) + 2 * g8 + 1);
+                    }
+                    hv[j][0] = a.x; hv[j][1] = a.y; hv[j][2] = a.z; hv[j][3] = a.w;
+                    hv[j][4] = b.x; hv[j][5] = b.y; hv[j][6] = b.z; hv[j][7] = b.w;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        mx = fmaxf(mx, fabsf(hv[j][q]));
+                        sum += hv[j][q];
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+                }
+                if (lane == 0) {
+                    s_part[warp * 2] = mx;
+                    s_part[warp * 2 + 1] = sum;
+                }
+                __syncthreads();
+                if (tid == 0) {   // fixed order: the sums do not depend on scheduling
+                    float bm = 0.0f, bs = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                        bm = fmaxf(bm, s_part[w * 2]);
+                        bs += s_part[w * 2 + 1];
+                    }
+                    s_mx[0] = bm;
+                    s_rs[0] = bs;
+                }
+                __syncthreads();
+            } else {
+                frag::scan_rows<NT, MULTI ? 4 : 1>(p.act, p.M, p.K, vec_ok, s_part, s_mx, s_rs);
+            }
             if (tid < p.M) {
                 const float bm = s_mx[tid];
                 s_dq[tid] = (bm > 0.0f && isfinite(bm)) ? bm / 16256.0f : 1.0f;
@@ -329,6 +380,26 @@ qmm_mma8_kernel(P8 p) {
                         }
                     }
                 }
+            }
+        } else if (kCanHold && held) {
+            const float inv = 1.0f / s_dq[0];
+#pragma unroll
+            for (int j = 0; j < kHeld; ++j) {
+                const int g8 = tid + j * NT;
+                if (g8 * 8 >= kc_len) continue;   // (beyond K the held values are zero: the padding of the last block)
+                uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+                for (int q8 = 0; q8 < 8; ++q8) {
+                    int q = __float2int_rn(hv[j][q8] * inv);
+                    q = max(-16256, min(16256, q));
+                    const int h = (q + 64) >> 7;
+                    const int pos = inner_pos8<FMT>(q8);
+                    hi[pos >> 2] |= (uint32_t)(h & 0xFF) << ((pos & 3) * 8);
+                    lo[pos >> 2] |= (uint32_t)((q - h * 128) & 0xFF) << ((pos & 3) * 8);
+                }
+                const int gp = group_pos8<FMT>(g8 * 8);
+                *reinterpret_cast<uint2 *>(s_act + gp) = make_uint2(hi[0], hi[1]);
+                *reinterpret_cast<uint2 *>(s_act + (size_t)RS + gp) = make_uint2(lo[0], lo[1]);
             }
         } else
         for (int m = 0; m < p.M; ++m) {
